@@ -68,8 +68,9 @@ class DeviceCache:
         self.v: List[torch.Tensor] = []
         for g, spec in enumerate(self.group_specs):
             shape = (len(members[g]), self.group_pages[g], spec.num_kv_heads, page_size, spec.head_dim)
+            value_dim = spec.head_dim if spec.value_dim is None else spec.value_dim
             self.k.append(torch.zeros(shape, dtype=dtype, device=device))
-            self.v.append(torch.zeros(shape, dtype=dtype, device=device))
+            self.v.append(torch.zeros(shape[:-1] + (value_dim,), dtype=dtype, device=device))
 
     @property
     def has_state(self) -> bool:
@@ -78,7 +79,8 @@ class DeviceCache:
     def bytes_per_token(self) -> int:
         total = 0
         for g, spec in enumerate(self.group_specs):
-            total += 2 * self.k[g].shape[0] * spec.num_kv_heads * spec.head_dim * self.k[g].element_size()
+            value_dim = spec.head_dim if spec.value_dim is None else spec.value_dim
+            total += self.k[g].shape[0] * spec.num_kv_heads * (spec.head_dim + value_dim) * self.k[g].element_size()
         return total
 
     def layer_view(self, cache_layer: int):

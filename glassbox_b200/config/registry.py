@@ -1,4 +1,4 @@
-"""One registry from an architecture's name (config.json ``architectures[0]``) to its model.
+"""One registry from an architecture's name (config.json ``architectures[0]``, or a plain ``architecture`` string) to its model.
 
 An ``Architecture`` is two functions and nothing else: ``parse`` turns the architecture's own
 config.json keys into a ``ModelConfig`` (the typed, per-layer description), and ``bind`` says
@@ -14,7 +14,7 @@ from __future__ import annotations
 import json
 import os
 from dataclasses import dataclass
-from typing import Callable, Dict, List
+from typing import Callable, Dict, List, Optional
 
 from .specs import ConfigError, ModelConfig
 
@@ -28,6 +28,9 @@ class Architecture:
     bind: Callable[[ModelConfig], dict]
     #: (keyword sizes) -> raw config.json dict, used by the random-weights mode and tests
     make_raw_config: Callable[..., dict] = None
+    #: True: ``parse`` takes a second argument, {tensor name: shape} of the weights file (None when there is no file
+    #: yet), for architectures some of whose sizes are written nowhere but in their tensors' shapes
+    sizes_from_tensors: bool = False
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
@@ -51,12 +54,21 @@ def get_architecture(name: str) -> Architecture:
             f"unknown architecture {name!r}; registered: {', '.join(architecture_names()) or '(none)'}") from None
 
 
-def parse_config(raw: dict) -> ModelConfig:
-    """Pick the architecture by ``architectures[0]`` and let it read its own keys."""
+def architecture_of(raw: dict) -> str:
+    """The architecture a config.json names: ``architectures[0]`` (the Hugging Face form) or a string ``architecture``."""
     archs = raw.get("architectures")
-    if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json: 'architectures' must be a non-empty list of names")
-    config = get_architecture(archs[0]).parse(raw)
+    if isinstance(archs, list) and archs and isinstance(archs[0], str):
+        return archs[0]
+    if archs is None and isinstance(raw.get("architecture"), str):
+        return raw["architecture"]
+    raise ConfigError("config.json: 'architectures' must be a non-empty list of names (or 'architecture' one name)")
+
+
+def parse_config(raw: dict, tensor_shapes: Optional[Dict[str, tuple]] = None) -> ModelConfig:
+    """Pick the architecture by name and let it read its own keys (and, if it asks for them, the shapes of the weights
+    file's tensors)."""
+    arch = get_architecture(architecture_of(raw))
+    config = arch.parse(raw, tensor_shapes) if arch.sizes_from_tensors else arch.parse(raw)
     config.validate()
     return config
 
@@ -72,4 +84,11 @@ def load_config(model_dir: str) -> ModelConfig:
         raise ConfigError(f"{path}: not valid JSON ({e})") from None
     if not isinstance(raw, dict):
         raise ConfigError(f"{path}: top level must be an object")
-    return parse_config(raw)
+    shapes = None
+    if get_architecture(architecture_of(raw)).sizes_from_tensors:
+        from ..weights.safetensors_io import SafetensorsFile
+        weights = os.path.join(model_dir, "model.safetensors")
+        if os.path.exists(weights):
+            with SafetensorsFile(weights) as st:
+                shapes = {name: tuple(st.shape(name)) for name in st.names()}
+    return parse_config(raw, shapes)

@@ -25,7 +25,8 @@ class RopeSpec:
     """Rotary position encoding over the first ``rotary_dim`` channels of each head.
 
     ``pairing`` "half" rotates channel i with channel i + rotary_dim/2 (the Hugging Face
-    weight layout, crates/glassbox-core/src/model.rs:110 with interleaved=false).
+    weight layout, crates/glassbox-core/src/model.rs:110 with interleaved=false); "interleaved" rotates channel 2i
+    with channel 2i + 1, at the angle position * theta^(-2i / rotary_dim) formed in float32 on the device.
     """
     theta: float
     rotary_dim: int
@@ -46,6 +47,13 @@ class RmsNormSpec:
 
 
 @dataclass(frozen=True)
+class UnitOffsetRmsNormSpec:
+    """RMSNorm whose stored weight lies around zero: the gain is 1 + weight."""
+    eps: float
+    kind: str = "rmsnorm_unit_offset"
+
+
+@dataclass(frozen=True)
 class GqaAttentionSpec:
     """Causal grouped-query attention over a paged key/value cache.
 
@@ -62,6 +70,53 @@ class GqaAttentionSpec:
 
 
 @dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Causal attention over a compressed cache: per token one latent of ``latent_dim`` numbers (RMS-normed with a plain
+    gain, ``latent_eps``), from which each head's unrotated key (``nope_dim``) and value (``value_dim``) are linear
+    maps, and one rotated key part of ``rope_dim`` numbers shared by all heads. A head's query is [nope_dim unrotated |
+    rope_dim rotated]. ``sink`` adds a learned logit per head to the softmax denominator. ``kv_source`` None: the layer
+    projects and stores its own latent; otherwise it has no such projection and reads the cache of the layer it names
+    (the schedule says which cache layer that is)."""
+    num_heads: int
+    nope_dim: int
+    rope_dim: int
+    value_dim: int
+    latent_dim: int
+    scale: float
+    position: Any
+    latent_eps: float
+    sink: bool = True
+    kv_source: Optional[int] = None
+    window: Optional[int] = None
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class ChannelDeltaSpec:
+    """A gated delta-rule mixer with a fixed-size state per head: S [key_dim, value_dim] decays per key channel, is
+    corrected towards the token's value along its key, and is read with the query. Queries and keys have
+    ``num_kv_heads`` heads shared by groups of value heads; q, k, v pass a causal convolution of ``conv_taps`` taps and
+    SiLU; the decay and the output gate come through low-rank maps (``decay_rank``, ``gate_rank``); the read-out is
+    RMS-normed per head (``norm_eps``) and gated."""
+    num_heads: int
+    num_kv_heads: int
+    key_dim: int
+    value_dim: int
+    conv_taps: int
+    decay_rank: int
+    gate_rank: int
+    norm_eps: float
+    kind: str = "channel_delta"
+
+
+@dataclass(frozen=True)
+class SquaredReluSpec:
+    """Dense feed-forward without a gate: down(relu(up(x))^2)."""
+    intermediate_size: int
+    kind: str = "relu2"
+
+
+@dataclass(frozen=True)
 class SwiGluSpec:
     """Dense gated feed-forward: down(silu(gate(x)) * up(x))."""
     intermediate_size: int
@@ -74,6 +129,20 @@ class EmbeddingSpec:
     (crates/glassbox-core/src/model.rs:228-231). Another kind (a scaled table, a learned position added to it) is
     another registered "embedding" part."""
     kind: str = "embedding"
+
+
+@dataclass(frozen=True)
+class ScaledEmbeddingSpec:
+    """Token embedding times a constant: the residual row of a token is its row of the table times ``scale``."""
+    scale: float
+    kind: str = "scaled_embedding"
+
+
+@dataclass(frozen=True)
+class ScaledLmHeadSpec:
+    """Output head whose logits carry a constant factor: logits = (hidden states times the head matrix) * ``scale``."""
+    scale: float
+    kind: str = "scaled_lm_head"
 
 
 @dataclass(frozen=True)
@@ -95,6 +164,10 @@ class LayerSpec:
     mixer_norm: Any
     ffn_norm: Any
     arrangement: str = "pre_norm"
+    #: "sandwich_norm" also norms each branch's output before it joins the residual: x += post(mixer(norm(x))),
+    #: x += post(ffn(norm(x))); there ``ffn`` may be None (a layer without a feed-forward)
+    mixer_post_norm: Any = None
+    ffn_post_norm: Any = None
 
 
 @dataclass(frozen=True)

@@ -1,0 +1,266 @@
+// A gated delta-rule mixer with one decay per head and key channel, and the short causal convolutions in front of it.
+//
+// Per head the state S is a [dk, dv] matrix of float32 that lives in the request's state slot. For each token, in order:
+//     S <- diag(g) S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+// with g = exp(-exp(A_log) * softplus(a + dt_bias)) per key channel, beta = sigmoid(b), q and k unit vectors
+// (x / sqrt(sum x^2 + 1e-6)) and q also times dk^(-1/2). Everything here is float32.
+//
+//   gb_short_conv        y[t, c] = silu(sum_j w[c, j] x[t - (taps-1) + j, c]), inputs before a portion's first row come
+//                        from the request's state slot (zeros for a fresh request)
+//   gb_short_conv_state  afterwards: the last taps-1 inputs of each request go to its slot
+//   gb_channel_delta     the recurrence; columns of S are independent, so a head is shared between blocks by columns
+#include "common.cuh"
+
+// ----------------------------------------------------------------------------------------------
+// Short convolution + SiLU. x: float32 [n, ldx] (channels 0..C-1), w: float32 [C, taps] (last column is the current
+// token's), state: float32, per slot `state_stride` numbers of which [taps-1, C] from `state_off` on (oldest first).
+// One thread per (row, channel).
+// ----------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) short_conv_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ w,
+                                                         float* __restrict__ y, long long ldy, const float* __restrict__ state,
+                                                         long long state_stride, long long state_off, const int* __restrict__ row_seq,
+                                                         const int* __restrict__ positions, const int* __restrict__ seq_first_row,
+                                                         const int* __restrict__ seq_slots, int n, int C, int taps, int num_slots,
+                                                         int* __restrict__ status) {
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    const int row = blockIdx.x;
+    const int ch = blockIdx.y * blockDim.x + threadIdx.x;
+    if (row >= n || ch >= C) return;
+    if (positions[row] < 0) return;
+    const int seq = row_seq[row];
+    const int r0 = seq_first_row[seq];
+    const int slot = seq_slots[seq];
+    if (slot < 0 || slot >= num_slots) {
+        atomicOr(status, GB_STATUS_BAD_SLOT);
+        return;
+    }
+    const float* st = state + (size_t)slot * state_stride + state_off;
+    float acc = 0.f;
+    for (int j = 0; j < taps; ++j) {
+        const int src = row - (taps - 1) + j;     // the row that holds this tap's input, if it is of this portion
+        float v;
+        if (src >= r0) v = x[(size_t)src * ldx + ch];
+        else v = st[(size_t)(taps - 1 - (r0 - src)) * C + ch];     // r0 - src inputs back from the portion's start
+        acc = fmaf(w[(size_t)ch * taps + j], v, acc);
+    }
+    y[(size_t)row * ldy + ch] = acc / (1.0f + expf(-acc));
+}
+
+// One thread per (sequence, channel): shift what the slot holds by the portion's length and append the portion's last inputs.
+__global__ void __launch_bounds__(256) short_conv_state_kernel(const float* __restrict__ x, long long ldx, float* __restrict__ state,
+                                                               long long state_stride, long long state_off,
+                                                               const int* __restrict__ seq_first_row, const int* __restrict__ seq_start_pos,
+                                                               const int* __restrict__ seq_slots, int S, int C, int taps, int num_slots) {
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    const int seq = blockIdx.x;
+    const int ch = blockIdx.y * blockDim.x + threadIdx.x;
+    if (seq >= S || ch >= C) return;
+    if (seq_start_pos[seq] < 0) return;
+    const int slot = seq_slots[seq];
+    if (slot < 0 || slot >= num_slots) return;
+    const int r0 = seq_first_row[seq], len = seq_first_row[seq + 1] - r0;
+    float* st = state + (size_t)slot * state_stride + state_off;
+    const int keep = taps - 1;
+    for (int i = 0; i < keep; ++i) {      // increasing i: a kept value moves to a lower index than any still to be read
+        const int p = len - keep + i;      // index within the portion
+        st[(size_t)i * C + ch] = p >= 0 ? x[(size_t)(r0 + p) * ldx + ch] : st[(size_t)(i + len) * C + ch];
+    }
+}
+
+GB_EXPORT int gb_short_conv(const float* x, long long ldx, const float* w, float* y, long long ldy, float* state,
+                            long long state_stride, long long state_off, const int* row_seq, const int* positions,
+                            const int* seq_first_row, const int* seq_start_pos, const int* seq_slots, int n, int S, int C, int taps,
+                            int num_slots, int update_state, int* status, cudaStream_t stream) {
+    GB_REQUIRE(n >= 0 && S >= 0 && C > 0 && taps >= 1 && taps <= 64, "gb_short_conv: bad sizes (taps %d)", taps);
+    if (n == 0 || S == 0) return 0;
+    dim3 grid(n, gb_ceil_div(C, 256));
+    gb_launch(GB_PDL_ELEMENTWISE, short_conv_kernel, grid, dim3(256), 0, stream, x, ldx, w, y, ldy, (const float*)state, state_stride,
+              state_off, row_seq, positions, seq_first_row, seq_slots, n, C, taps, num_slots, status);
+    int rc = gb_check_launch("gb_short_conv");
+    if (rc || !update_state || taps == 1) return rc;
+    dim3 grid2(S, gb_ceil_div(C, 256));
+    gb_launch(GB_PDL_ELEMENTWISE, short_conv_state_kernel, grid2, dim3(256), 0, stream, x, ldx, state, state_stride, state_off,
+              seq_first_row, seq_start_pos, seq_slots, S, C, taps, num_slots);
+    return gb_check_launch("gb_short_conv_state");
+}
+
+// ----------------------------------------------------------------------------------------------
+// The recurrence. Grid (sequences of the step, heads, column blocks); 128 threads. A thread owns DPT rows of one
+// column of S in registers: lane = column * NS + split, so the NS splits of a column are neighbouring lanes and the
+// two reductions over the key dimension are shuffles. Tokens are staged TC at a time in shared memory (q and k made
+// unit vectors, decays and beta evaluated) by all threads; the walk over the TC tokens needs no block barrier.
+// ----------------------------------------------------------------------------------------------
+constexpr int CD_THREADS = 128;
+constexpr float CD_UNIT_EPS = 1e-6f;
+
+struct ChannelDeltaArgs {
+    const float* qkv;       // [n, ldq]: q (kvh * dk), k (kvh * dk), v (heads * dv), after convolution and SiLU
+    long long ldq;
+    const float* beta;      // [n, ldb]: logits of beta, one per head
+    long long ldb;
+    const float* a;         // [n, lda]: decay logits before the bias, heads * dk
+    long long lda;
+    const float* dt_bias;   // [heads * dk]
+    const float* a_log;     // [heads]
+    float* state;           // per slot `state_stride` numbers; S is [heads, dk, dv] at the start
+    long long state_stride;
+    float* out;             // [n, heads * dv]: o before its norm
+    const int* seq_first_row;
+    const int* seq_start_pos;
+    const int* seq_slots;
+    int heads, kv_heads, dk, dv, ns, tc, num_slots, write_state;
+    int* status;
+};
+
+template <int DPT>
+__global__ void __launch_bounds__(CD_THREADS) channel_delta_kernel(ChannelDeltaArgs p) {
+    extern __shared__ __align__(16) float cd_smem[];
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    const int seq = blockIdx.x, head = blockIdx.y;
+    if (p.seq_start_pos[seq] < 0) return;
+    const int slot = p.seq_slots[seq];
+    if (slot < 0 || slot >= p.num_slots) {
+        if (threadIdx.x == 0) atomicOr(p.status, GB_STATUS_BAD_SLOT);
+        return;
+    }
+    const int r0 = p.seq_first_row[seq], r1 = p.seq_first_row[seq + 1];
+    const int NS = p.ns, TC = p.tc, dk = p.dk, dv = p.dv;
+    const int cols = CD_THREADS / NS;                     // columns of S per block
+    const int split = threadIdx.x % NS, col_local = threadIdx.x / NS;
+    const int col = blockIdx.z * cols + col_local;
+    const bool live = col < dv;
+    const int kvh = head / (p.heads / p.kv_heads);
+    constexpr int PAD = DPT + 4;                          // a split's numbers start 16-byte aligned, on other banks than its neighbours'
+    const int row_w = NS * PAD;
+    float* qs = cd_smem;                                  // [TC][row_w]
+    float* ks = qs + (size_t)TC * row_w;
+    float* gs = ks + (size_t)TC * row_w;
+    float* vs = gs + (size_t)TC * row_w;                  // [TC][cols]
+    float* bs = vs + (size_t)TC * cols;                   // [TC]
+
+    float S[DPT];
+    float* sbase = p.state + (size_t)slot * p.state_stride + (size_t)head * dk * dv;
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        const int d = split * DPT + i;
+        S[i] = (live && d < dk) ? sbase[(size_t)d * dv + col] : 0.f;
+    }
+    const float decay_rate = expf(p.a_log[head]);
+    const float q_scale = 1.0f / sqrtf((float)dk);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    for (int c0 = r0; c0 < r1; c0 += TC) {
+        const int nt = min(TC, r1 - c0);
+        __syncthreads();       // the walk over the chunk before is done with the staged numbers
+        // staging: a warp per token
+        for (int t = warp; t < nt; t += CD_THREADS / 32) {
+            const size_t row = (size_t)(c0 + t);
+            const float* qrow = p.qkv + row * p.ldq + (size_t)kvh * dk;
+            const float* krow = p.qkv + row * p.ldq + (size_t)(p.kv_heads + kvh) * dk;
+            const float* arow = p.a + row * p.lda + (size_t)head * dk;
+            float sq = 0.f, sk = 0.f;
+            for (int d = lane; d < dk; d += 32) {
+                const float qv = qrow[d], kv = krow[d];
+                sq = fmaf(qv, qv, sq);
+                sk = fmaf(kv, kv, sk);
+            }
+            sq = gb_warp_sum(sq);
+            sk = gb_warp_sum(sk);
+            const float iq = q_scale / sqrtf(sq + CD_UNIT_EPS), ik = 1.0f / sqrtf(sk + CD_UNIT_EPS);
+            for (int d = lane; d < NS * DPT; d += 32) {
+                const int at = t * row_w + (d / DPT) * PAD + d % DPT;
+                if (d < dk) {
+                    const float z = arow[d] + p.dt_bias[(size_t)head * dk + d];
+                    const float sp = z > 20.f ? z : log1pf(expf(z));
+                    qs[at] = qrow[d] * iq;
+                    ks[at] = krow[d] * ik;
+                    gs[at] = expf(-decay_rate * sp);
+                } else {
+                    qs[at] = 0.f;
+                    ks[at] = 0.f;
+                    gs[at] = 1.f;
+                }
+            }
+            if (lane == 0) bs[t] = 1.0f / (1.0f + expf(-p.beta[row * p.ldb + head]));
+        }
+        for (int idx = threadIdx.x; idx < nt * cols; idx += CD_THREADS) {
+            const int t = idx / cols, cl = idx % cols;
+            const int cc = blockIdx.z * cols + cl;
+            vs[t * cols + cl] = cc < dv ? p.qkv[(size_t)(c0 + t) * p.ldq + (size_t)2 * p.kv_heads * dk + (size_t)head * dv + cc] : 0.f;
+        }
+        __syncthreads();
+        for (int t = 0; t < nt; ++t) {
+            const float4* g4 = reinterpret_cast<const float4*>(gs + t * row_w + split * PAD);
+            const float4* k4 = reinterpret_cast<const float4*>(ks + t * row_w + split * PAD);
+            const float4* q4 = reinterpret_cast<const float4*>(qs + t * row_w + split * PAD);
+            float kk[DPT];
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPT / 4; ++i) {
+                const float4 g = g4[i], k = k4[i];
+                kk[4 * i] = k.x; kk[4 * i + 1] = k.y; kk[4 * i + 2] = k.z; kk[4 * i + 3] = k.w;
+                S[4 * i] *= g.x; S[4 * i + 1] *= g.y; S[4 * i + 2] *= g.z; S[4 * i + 3] *= g.w;
+                a0 = fmaf(S[4 * i], k.x, a0);
+                a1 = fmaf(S[4 * i + 1], k.y, a1);
+                a2 = fmaf(S[4 * i + 2], k.z, a2);
+                a3 = fmaf(S[4 * i + 3], k.w, a3);
+            }
+            float sk = (a0 + a1) + (a2 + a3);
+            for (int o = 1; o < NS; o <<= 1) sk += __shfl_xor_sync(0xffffffffu, sk, o);
+            const float u = bs[t] * (vs[t * cols + col_local] - sk);
+            a0 = a1 = a2 = a3 = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPT / 4; ++i) {
+                const float4 q = q4[i];
+                S[4 * i] = fmaf(kk[4 * i], u, S[4 * i]);
+                S[4 * i + 1] = fmaf(kk[4 * i + 1], u, S[4 * i + 1]);
+                S[4 * i + 2] = fmaf(kk[4 * i + 2], u, S[4 * i + 2]);
+                S[4 * i + 3] = fmaf(kk[4 * i + 3], u, S[4 * i + 3]);
+                a0 = fmaf(S[4 * i], q.x, a0);
+                a1 = fmaf(S[4 * i + 1], q.y, a1);
+                a2 = fmaf(S[4 * i + 2], q.z, a2);
+                a3 = fmaf(S[4 * i + 3], q.w, a3);
+            }
+            float o = (a0 + a1) + (a2 + a3);
+            for (int w = 1; w < NS; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
+            if (split == 0 && live) p.out[(size_t)(c0 + t) * p.heads * dv + (size_t)head * dv + col] = o;
+        }
+    }
+    if (p.write_state) {
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) {
+            const int d = split * DPT + i;
+            if (live && d < dk) sbase[(size_t)d * dv + col] = S[i];
+        }
+    }
+}
+
+GB_EXPORT int gb_channel_delta(const float* qkv, long long ldq, const float* beta, long long ldb, const float* a, long long lda,
+                               const float* dt_bias, const float* a_log, float* state, long long state_stride, float* out,
+                               const int* seq_first_row, const int* seq_start_pos, const int* seq_slots, int S, int heads,
+                               int kv_heads, int dk, int dv, int num_slots, int write_state, int* status, cudaStream_t stream) {
+    GB_REQUIRE(S >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "gb_channel_delta: heads %d must be a multiple of key heads %d",
+               heads, kv_heads);
+    GB_REQUIRE(dk > 0 && dk <= 1024 && dv > 0, "gb_channel_delta: a key size of %d is outside 1..1024", dk);
+    if (S == 0) return 0;
+    const int dpt = dk <= 128 ? 16 : 32;
+    int ns = 1;
+    while (ns * dpt < dk) ns *= 2;
+    const int cols = CD_THREADS / ns;
+    const int per_token = (3 * ns * (dpt + 4) + cols + 1) * (int)sizeof(float);
+    int tc = (40 * 1024) / per_token;
+    if (tc > 16) tc = 16;
+    if (tc < 1) tc = 1;
+    ChannelDeltaArgs p = {qkv, ldq, beta, ldb, a, lda, dt_bias, a_log, state, state_stride, out, seq_first_row, seq_start_pos,
+                          seq_slots, heads, kv_heads, dk, dv, ns, tc, num_slots, write_state, status};
+    dim3 grid(S, heads, gb_ceil_div(dv, cols));
+    const size_t smem = (size_t)tc * per_token;
+    if (dpt == 16)
+        gb_launch(GB_PDL_ATTENTION, channel_delta_kernel<16>, grid, dim3(CD_THREADS), smem, stream, p);
+    else
+        gb_launch(GB_PDL_ATTENTION, channel_delta_kernel<32>, grid, dim3(CD_THREADS), smem, stream, p);
+    return gb_check_launch("gb_channel_delta");
+}

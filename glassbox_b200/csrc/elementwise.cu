@@ -4,11 +4,11 @@
 #include "common.cuh"
 
 // ----------------------------------------------------------------------------------------------
-// Embedding: x[i, :] = table[tokens[i], :]   (crates/glassbox-core/src/model.rs:228-231)
+// Embedding: x[i, :] = table[tokens[i], :] * scale   (crates/glassbox-core/src/model.rs:228-231; scale 1 there)
 // ----------------------------------------------------------------------------------------------
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ x,
-                             int n, int d, int vocab, int* __restrict__ status) {
+                             int n, int d, int vocab, float scale, int* __restrict__ status) {
     int row = blockIdx.x;
     if (row >= n) return;
     int tok = tokens[row];
@@ -18,19 +18,19 @@ __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict
         return;
     }
     const TW* src = table + (size_t)tok * d;
-    for (int j = threadIdx.x; j < d; j += blockDim.x) x[(size_t)row * d + j] = gb_to_float(src[j]);
+    for (int j = threadIdx.x; j < d; j += blockDim.x) x[(size_t)row * d + j] = gb_to_float(src[j]) * scale;
 }
 
 GB_EXPORT int gb_embed(const void* table, int table_dtype, const int* tokens, float* x, int n, int d, int vocab,
-                       int* status, cudaStream_t stream) {
+                       float scale, int* status, cudaStream_t stream) {
     GB_REQUIRE(n >= 0 && d > 0 && vocab > 0, "gb_embed: bad sizes n=%d d=%d vocab=%d", n, d, vocab);
     if (n == 0) return 0;
     int threads = d >= 256 ? 256 : 128;
     if (table_dtype == GB_F32)
-        embed_kernel<float><<<n, threads, 0, stream>>>((const float*)table, tokens, x, n, d, vocab, status);
+        embed_kernel<float><<<n, threads, 0, stream>>>((const float*)table, tokens, x, n, d, vocab, scale, status);
     else if (table_dtype == GB_BF16)
         embed_kernel<__nv_bfloat16><<<n, threads, 0, stream>>>((const __nv_bfloat16*)table, tokens, x, n, d, vocab,
-                                                                status);
+                                                                scale, status);
     else
         GB_REQUIRE(false, "gb_embed: unsupported table dtype %d", table_dtype);
     return gb_check_launch("gb_embed");
@@ -281,26 +281,28 @@ GB_EXPORT int gb_swiglu(const void* gate_up, void* act, int dtype, int n, int in
 // group (crates/glassbox-core/src/kv.rs:189-196). Layers are `layer_stride` elements apart.
 // ----------------------------------------------------------------------------------------------
 __global__ void copy_pages_kernel(uint4* __restrict__ k, uint4* __restrict__ v, const int* __restrict__ pairs,
-                                  int n_pairs, long long page_vec, long long layer_vec, int layers) {
+                                  int n_pairs, long long page_vec, long long layer_vec, long long v_page_vec,
+                                  long long v_layer_vec, int layers) {
     int pair = blockIdx.x, layer = blockIdx.y;
     if (pair >= n_pairs || layer >= layers) return;
     long long src = pairs[2 * pair], dst = pairs[2 * pair + 1];
     uint4* ks = k + layer * layer_vec + src * page_vec;
     uint4* kd = k + layer * layer_vec + dst * page_vec;
-    uint4* vs = v + layer * layer_vec + src * page_vec;
-    uint4* vd = v + layer * layer_vec + dst * page_vec;
-    for (long long i = threadIdx.x; i < page_vec; i += blockDim.x) {
-        kd[i] = ks[i];
-        vd[i] = vs[i];
-    }
+    uint4* vs = v + layer * v_layer_vec + src * v_page_vec;
+    uint4* vd = v + layer * v_layer_vec + dst * v_page_vec;
+    for (long long i = threadIdx.x; i < page_vec; i += blockDim.x) kd[i] = ks[i];
+    if (v == nullptr) return;     // a group that keeps one tensor per token has no second pool
+    for (long long i = threadIdx.x; i < v_page_vec; i += blockDim.x) vd[i] = vs[i];
 }
 
 GB_EXPORT int gb_copy_pages(void* kcache, void* vcache, const int* pairs, int n_pairs, long long page_bytes,
-                            long long layer_bytes, int layers, cudaStream_t stream) {
-    GB_REQUIRE(page_bytes % 16 == 0 && layer_bytes % 16 == 0, "gb_copy_pages: page bytes must be a multiple of 16");
+                            long long layer_bytes, long long v_page_bytes, long long v_layer_bytes, int layers,
+                            cudaStream_t stream) {
+    GB_REQUIRE(page_bytes % 16 == 0 && layer_bytes % 16 == 0 && v_page_bytes % 16 == 0 && v_layer_bytes % 16 == 0,
+               "gb_copy_pages: page bytes must be a multiple of 16");
     if (n_pairs == 0 || layers == 0) return 0;
     dim3 grid(n_pairs, layers);
     copy_pages_kernel<<<grid, 256, 0, stream>>>((uint4*)kcache, (uint4*)vcache, pairs, n_pairs, page_bytes / 16,
-                                                layer_bytes / 16, layers);
+                                                layer_bytes / 16, v_page_bytes / 16, v_layer_bytes / 16, layers);
     return gb_check_launch("gb_copy_pages");
 }

@@ -125,6 +125,8 @@ class StepContext:
         self.next_norm = None             # the norm that will read the residual after the product that adds into it next
         self.norm_after_layer = None      # the norm that will read the residual after the layer that runs now
         self.prepared_norm = None         # parts.base.PreparedNorm: what the last such product left for that norm
+        # A wiring that norms a branch before it joins the residual hands the part a blank buffer instead of the residual:
+        self.overwrite_output = False     # True: the part's last product stores into the tensor it was given, not adds
 
     def scratch(self, name: str, shape, dtype: Optional[torch.dtype] = None, grow: bool = False) -> torch.Tensor:
         return (self._grow if grow else self._scratch).get(name, shape, dtype, grow)

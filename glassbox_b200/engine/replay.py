@@ -131,6 +131,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--max-requests", type=int, default=4, help="state slots: the most requests that are live at any time")
     ap.add_argument("--max-batch-tokens", type=int, default=0,
                     help="most tokens in one step (default: max-tokens)")
     ap.add_argument("--share-prefixes", action="store_true",
@@ -144,7 +145,7 @@ def main(argv=None) -> int:
         return 2
     pool_tokens = -(-args.max_tokens // 64) * 64
     engine = Engine(args.model, args.dtype, cache_tokens=pool_tokens, page_size=args.page_size,
-                    max_batch_tokens=args.max_batch_tokens or max(pool_tokens, 64), max_requests=8,
+                    max_batch_tokens=args.max_batch_tokens or max(pool_tokens, 64), max_requests=args.max_requests,
                     share_prefixes=args.share_prefixes)
     replayer = Replayer(engine)
     for line in sys.stdin:

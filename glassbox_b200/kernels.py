@@ -32,11 +32,11 @@ _c = ctypes
 _P, _I, _LL, _F = _c.c_void_p, _c.c_int, _c.c_longlong, _c.c_float
 
 _SIGNATURES = {
-    "gb_embed": [_P, _I, _P, _P, _I, _I, _I, _P, _P],
+    "gb_embed": [_P, _I, _P, _P, _I, _I, _I, _F, _P, _P],
     "gb_rmsnorm": [_P, _P, _P, _P, _I, _I, _I, _F, _P],
     "gb_rope_kv_write": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _LL, _I, _P, _P],
     "gb_swiglu": [_P, _P, _I, _I, _I, _P],
-    "gb_copy_pages": [_P, _P, _P, _I, _LL, _LL, _I, _P],
+    "gb_copy_pages": [_P, _P, _P, _I, _LL, _LL, _LL, _LL, _I, _P],
     "gb_gemm_simt": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _LL, _LL, _LL, _P],
     "gb_attention_rows": [_P, _LL, _P, _LL, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
     "gb_sample": [_P, _LL, _P, _P, _P, _P, _I, _P, _P, _I, _I, _P],
@@ -75,6 +75,14 @@ _SIGNATURES = {
     "gb_program_launch_with_absent_blocks": [_P, _I, _I, _I, _I, _I, _I, _P, _P, _I, _LL, _P],
     "gb_program_launch_traced": [_P, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P],
     "gb_step_io": [_P, _P, _LL, _P, _P, _P, _LL, _P],
+    "gb_rmsnorm_add": [_P, _LL, _P, _P, _LL, _I, _I, _F, _P],
+    "gb_relu2": [_P, _P, _I, _LL, _P],
+    "gb_scale": [_P, _LL, _F, _P],
+    "gb_gated_head_norm": [_P, _P, _LL, _P, _P, _I, _I, _I, _I, _F, _P],
+    "gb_latent_kv_write": [_P, _LL, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
+    "gb_latent_attention_rows": [_P, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
+    "gb_short_conv": [_P, _LL, _P, _P, _LL, _P, _LL, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
+    "gb_channel_delta": [_P, _LL, _P, _LL, _P, _LL, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "gb_program_op_bytes": [],
     "gb_program_max_rows": [],
 }
@@ -301,12 +309,12 @@ def check_status(status: torch.Tensor) -> None:
 
 
 # ------------------------------------------------------------------------------------------ ops
-def embed(table: torch.Tensor, tokens: torch.Tensor, x: torch.Tensor, status: torch.Tensor) -> None:
-    """x[i, :] = table[tokens[i], :] as float32."""
+def embed(table: torch.Tensor, tokens: torch.Tensor, x: torch.Tensor, status: torch.Tensor, scale: float = 1.0) -> None:
+    """x[i, :] = table[tokens[i], :] * scale as float32."""
     _cuda(table, tokens, x, status)
     n, d = x.shape
     assert tokens.dtype == torch.int32 and x.dtype == torch.float32 and x.is_contiguous() and table.is_contiguous()
-    _call("gb_embed", _ptr(table), _dt(table), _ptr(tokens), _ptr(x), n, d, table.shape[0], _ptr(status), _stream())
+    _call("gb_embed", _ptr(table), _dt(table), _ptr(tokens), _ptr(x), n, d, table.shape[0], float(scale), _ptr(status), _stream())
 
 
 def rmsnorm(x: torch.Tensor, gain: torch.Tensor, out: torch.Tensor, eps: float,
@@ -348,8 +356,10 @@ def copy_pages(kcache: torch.Tensor, vcache: torch.Tensor, pairs: torch.Tensor) 
     layers = kcache.shape[0]
     layer_bytes = kcache.stride(0) * kcache.element_size()
     page_bytes = kcache.stride(1) * kcache.element_size()
-    _call("gb_copy_pages", _ptr(kcache), _ptr(vcache), _ptr(pairs), pairs.shape[0], page_bytes, layer_bytes, layers,
-          _stream())
+    has_v = vcache.numel() > 0       # (a group that keeps one tensor per token has an empty second pool)
+    _call("gb_copy_pages", _ptr(kcache), _ptr(vcache) if has_v else 0, _ptr(pairs), pairs.shape[0], page_bytes, layer_bytes,
+          vcache.stride(1) * vcache.element_size() if has_v else 0, vcache.stride(0) * vcache.element_size() if has_v else 0,
+          layers, _stream())
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool = False) -> None:
@@ -805,3 +815,111 @@ def resolve_tokens(tokens: torch.Tensor, token_slots: torch.Tensor, last_token: 
     _cuda(tokens, token_slots, last_token)
     assert tokens.dtype == token_slots.dtype == last_token.dtype == torch.int32 and token_slots.numel() >= tokens.numel()
     _call("gb_resolve_tokens", _ptr(tokens), _ptr(token_slots), _ptr(last_token), tokens.numel(), last_token.numel(), _stream())
+
+
+# ------------------------------------------------------------------ branches that are normed before they join the residual
+def rmsnorm_add(y: torch.Tensor, gain: torch.Tensor, x: torch.Tensor, eps: float) -> None:
+    """x[r, :] += gain * y[r, :] / sqrt(mean(y[r, :]^2) + eps); everything float32."""
+    _cuda(y, gain, x)
+    n, d = x.shape
+    assert y.shape == (n, d) and y.dtype == x.dtype == gain.dtype == torch.float32 and gain.numel() == d
+    assert y.stride(1) == 1 and x.stride(1) == 1
+    _call("gb_rmsnorm_add", _ptr(y), y.stride(0), _ptr(gain), _ptr(x), x.stride(0), n, d, float(eps), _stream())
+
+
+def relu2(h: torch.Tensor, out: torch.Tensor) -> None:
+    """out = max(h, 0)^2, element by element."""
+    _cuda(h, out)
+    assert h.shape == out.shape and h.dtype == out.dtype and h.is_contiguous() and out.is_contiguous()
+    _call("gb_relu2", _ptr(h), _ptr(out), _dt(out), h.numel(), _stream())
+
+
+def scale_(t: torch.Tensor, s: float) -> None:
+    """t *= s in place (float32)."""
+    _cuda(t)
+    assert t.dtype == torch.float32 and t.is_contiguous()
+    _call("gb_scale", _ptr(t), t.numel(), float(s), _stream())
+
+
+def gated_head_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, heads: int, eps: float) -> None:
+    """out[r, h, :] = weight * o[r, h, :] / sqrt(mean(o[r, h, :]^2) + eps) * sigmoid(gate[r, h, :]); o, gate, weight
+    float32 (gate may be a column slice of a wider tensor)."""
+    _cuda(o, gate, weight, out)
+    n, hv = o.shape
+    v = hv // heads
+    assert o.dtype == gate.dtype == weight.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous()
+    assert gate.shape == (n, hv) and gate.stride(1) == 1 and out.shape == (n, hv) and weight.numel() == v
+    _call("gb_gated_head_norm", _ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), _ptr(out), _dt(out), n, heads, v, float(eps),
+          _stream())
+
+
+# ------------------------------------------------------------------------------- attention over a latent cache
+def latent_kv_write(proj: torch.Tensor, kv_col: int, qabs: torch.Tensor, cache: torch.Tensor, latent_gain: Optional[torch.Tensor],
+                    inv_freq: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, heads: int, dq: int, r: int, c: int,
+                    rot_dims: int, eps: float, write_kv: bool, status: torch.Tensor) -> None:
+    """Rotate every head's rotated query part of ``proj`` [n, >= heads * (dq + r)] into ``qabs`` [n, heads, c + r][..., c:];
+    with ``write_kv`` also RMS-norm the raw latent (columns kv_col .. kv_col + c), rotate the raw shared key part behind it
+    and store both at each row's slot of ``cache`` [pages, 1, page_size, c + r]."""
+    _cuda(proj, qabs, cache, latent_gain, inv_freq, positions, slots, status)
+    n = proj.shape[0]
+    assert proj.stride(1) == 1 and qabs.is_contiguous() and cache.is_contiguous() and proj.dtype == qabs.dtype == cache.dtype
+    assert qabs.shape[0] == n and qabs.numel() == n * heads * (c + r) and cache.shape[-1] == c + r
+    assert inv_freq.dtype == torch.float32 and inv_freq.numel() >= rot_dims // 2
+    num_slots = cache.numel() // (c + r)
+    _call("gb_latent_kv_write", _ptr(proj), proj.stride(0), kv_col, _ptr(qabs), _ptr(cache), _dt(proj), _ptr(latent_gain),
+          _ptr(inv_freq), _ptr(positions), _ptr(slots), n, heads, dq, r, c, rot_dims, num_slots, float(eps),
+          1 if write_kv else 0, _ptr(status), _stream())
+
+
+def latent_attention_rows(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor,
+                          row_seq: torch.Tensor, positions: torch.Tensor, sink: Optional[torch.Tensor], heads: int, c: int, r: int,
+                          page_size: int, scale: float, window: Optional[int], status: torch.Tensor) -> None:
+    """out[row, head, :c] = sum_j p_j latent_j with p the softmax (with an optional sink logit per head in the denominator)
+    of scale * q[row, head, :] . cache_row_j over the row's visible tokens; one warp per (row, head), float32 arithmetic."""
+    _cuda(q, out, cache, block_tables, row_seq, positions, sink, status)
+    n = q.shape[0]
+    assert q.is_contiguous() and out.is_contiguous() and cache.is_contiguous() and q.dtype == out.dtype == cache.dtype
+    assert q.numel() == n * heads * (c + r) and out.numel() == n * heads * c and cache.shape[-1] == c + r
+    num_pages = cache.numel() // ((c + r) * page_size)
+    _call("gb_latent_attention_rows", _ptr(q), _ptr(out), _dt(q), _ptr(cache), _ptr(block_tables), block_tables.shape[1],
+          _ptr(row_seq), _ptr(positions), _ptr(sink), n, heads, c, r, page_size, num_pages, float(scale),
+          int(window) if window else 0, _ptr(status), _stream())
+
+
+# ------------------------------------------------------------------------------------- recurrent state mixers
+def short_conv(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, state: torch.Tensor, state_off: int, ctx_row_seq: torch.Tensor,
+               positions: torch.Tensor, seq_first_row: torch.Tensor, seq_start_pos: torch.Tensor, seq_slots: torch.Tensor,
+               update_state: bool, status: torch.Tensor) -> None:
+    """y[t, c] = silu(sum_j w[c, j] * x[t - (taps - 1) + j, c]) along each request's rows; inputs from before the step come
+    from (and, with ``update_state``, the last taps - 1 inputs go to) the request's slot of ``state`` [slots, numbers],
+    at ``state_off``, laid out [taps - 1, channels]. x may be a column slice; float32."""
+    _cuda(x, w, y, state, ctx_row_seq, positions, seq_first_row, seq_start_pos, seq_slots, status)
+    n, C = y.shape
+    taps = w.shape[1]
+    assert x.shape == (n, C) and x.stride(1) == 1 and y.stride(1) == 1 and w.shape == (C, taps) and w.is_contiguous()
+    assert x.dtype == y.dtype == w.dtype == state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous()
+    assert state_off + (taps - 1) * C <= state.shape[1]
+    _call("gb_short_conv", _ptr(x), x.stride(0), _ptr(w), _ptr(y), y.stride(0), _ptr(state), state.stride(0), state_off,
+          _ptr(ctx_row_seq), _ptr(positions), _ptr(seq_first_row), _ptr(seq_start_pos), _ptr(seq_slots), n, seq_start_pos.shape[0],
+          C, taps, state.shape[0], 1 if update_state else 0, _ptr(status), _stream())
+
+
+def channel_delta(qkv: torch.Tensor, beta: torch.Tensor, a: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor,
+                  state: torch.Tensor, out: torch.Tensor, seq_first_row: torch.Tensor, seq_start_pos: torch.Tensor,
+                  seq_slots: torch.Tensor, heads: int, kv_heads: int, dk: int, dv: int, write_state: bool,
+                  status: torch.Tensor) -> None:
+    """The gated delta rule with a decay per head and key channel, token by token along each request's rows, from and to
+    the request's slot of ``state`` [slots, numbers] (S = [heads, dk, dv] first). qkv float32 [n, 2 * kv_heads * dk + heads * dv]
+    (q, k, v after their convolutions), beta [n, heads] and a [n, heads * dk] logits (column slices allowed);
+    out float32 [n, heads * dv] is the read-out before its norm."""
+    _cuda(qkv, beta, a, dt_bias, a_log, state, out, seq_first_row, seq_start_pos, seq_slots, status)
+    n = qkv.shape[0]
+    for t in (qkv, beta, a, dt_bias, a_log, state, out):
+        assert t.dtype == torch.float32
+    assert qkv.shape[1] == 2 * kv_heads * dk + heads * dv and qkv.stride(1) == 1 and beta.shape == (n, heads)
+    assert a.shape == (n, heads * dk) and a.stride(1) == 1 and beta.stride(1) == 1 and out.shape == (n, heads * dv)
+    assert out.is_contiguous() and state.dim() == 2 and state.is_contiguous() and state.shape[1] >= heads * dk * dv
+    assert dt_bias.numel() == heads * dk and a_log.numel() == heads
+    _call("gb_channel_delta", _ptr(qkv), qkv.stride(0), _ptr(beta), beta.stride(0), _ptr(a), a.stride(0), _ptr(dt_bias),
+          _ptr(a_log), _ptr(state), state.stride(0), _ptr(out), _ptr(seq_first_row), _ptr(seq_start_pos), _ptr(seq_slots),
+          seq_start_pos.shape[0], heads, kv_heads, dk, dv, state.shape[0], 1 if write_state else 0, _ptr(status), _stream())

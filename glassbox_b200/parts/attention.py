@@ -34,6 +34,8 @@ class GqaAttention(Mixer):
         self.nh, self.nkv, self.hd = s.num_heads, s.num_kv_heads, s.head_dim
         self.qd, self.kvd = self.nh * self.hd, self.nkv * self.hd
         self.position = build_part("position", s.position)
+        if getattr(self.position, "pairing", "half") != "half":
+            raise ValueError("grouped-query attention rotates channel i with channel i + rotary_dim/2 only")
 
     def sub_parts(self):
         return {"position": self.position}

@@ -39,10 +39,13 @@ from ..weights.binding import ParamSpec
 class PagedKvSpec:
     """A mixer that keeps keys and values per token, in pages. Layers with equal specs share a
     cache group (one block table, one page pool). ``window`` None keeps every token; an integer
-    keeps only the last ``window`` tokens, and pages behind the window are given back."""
+    keeps only the last ``window`` tokens, and pages behind the window are given back. ``value_dim`` is the size of the
+    second tensor per token and head (None: ``head_dim``; 0: the mixer keeps one tensor per token, the second pool is
+    empty)."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -92,6 +95,13 @@ class Norm(Part):
         """(gain, eps) if this norm is a plain RMSNorm that a GEMM kernel may apply on the way in, else
         None (the norm then always runs as its own kernel)."""
         return None
+
+    def add_normed(self, ctx, y, x) -> None:
+        """x += norm(y), both float32 [n, d]: a branch whose output is normed before it joins the residual stream.
+        The default goes through ``forward``; norms with a kernel for it override this."""
+        tmp = ctx.scratch("normed_branch", tuple(y.shape), torch.float32)
+        self.forward(ctx, y, tmp)
+        x += tmp
 
 
 class PreparedNorm:
@@ -150,6 +160,10 @@ class Position(Part):
 class Mixer(Part):
     #: set by parts whose ``forward`` can take a ``DeferredNorm`` as ``h``
     accepts_deferred_input = False
+    #: set by parts that look at ``ctx.overwrite_output``: when a wiring hands them a blank branch buffer instead of the
+    #: residual stream it sets that flag, and the part's last product then stores instead of adding (the buffer need
+    #: not be cleared first). Parts that leave this False always add, into a buffer the wiring has cleared.
+    can_overwrite_output = False
 
     def cache_spec(self):
         return None
@@ -165,6 +179,7 @@ class Mixer(Part):
 
 class FeedForward(Part):
     accepts_deferred_input = False
+    can_overwrite_output = False      # as ``Mixer.can_overwrite_output``
 
     def forward(self, ctx, h, residual) -> None:
         raise NotImplementedError

@@ -1,0 +1,97 @@
+"""A gated delta-rule mixer with one decay per head and key channel.
+
+h -> one stacked product gives q and k (num_kv_heads x key_dim each), v (num_heads x value_dim), the inputs of the two
+low-rank maps (decay, output gate) and beta's logits. q, k, v pass a short causal convolution along the request's
+tokens (its last taps - 1 inputs live in the request's state slot) and SiLU; q and k become unit vectors per head, q
+also times key_dim^(-1/2). Per head, with S [key_dim, value_dim] from the request's state slot, token by token:
+
+    S <- diag(g) S,  g = exp(-exp(A_log) * softplus(W_a2 (W_a1 h) + dt_bias))   (one decay per key channel)
+    u = beta (v - S^T k),  beta = sigmoid(W_b h)
+    S <- S + k u^T
+    o = S^T q                                                                   (the read-out sees the token's own write)
+
+o is RMS-normed per head (gain shared by heads), times sigmoid(W_g2 (W_g1 h)), and projected by W_o. The state, the
+decays, beta, the unit vectors and the norm are float32 whatever the activation dtype: the stacked product and the two
+second-level products write float32.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..weights.binding import ParamSpec
+from .base import Mixer, StateSpec, register_part
+from .linear import linear
+
+
+class ChannelDelta(Mixer):
+    accepts_deferred_input = True
+    launches_through_kernels_only = True
+    can_overwrite_output = True
+
+    def __init__(self, spec, *, hidden_size: int):
+        super().__init__(spec)
+        s = spec
+        if s.num_heads <= 0 or s.num_kv_heads <= 0 or s.num_heads % s.num_kv_heads:
+            raise ValueError(f"num_heads {s.num_heads} is not a multiple of num_kv_heads {s.num_kv_heads}")
+        if not 0 < s.key_dim <= 1024 or s.value_dim <= 0:
+            raise ValueError(f"key_dim {s.key_dim} must lie in 1..1024 and value_dim {s.value_dim} be positive")
+        if not 1 <= s.conv_taps <= 64:
+            raise ValueError(f"conv_taps {s.conv_taps} must lie in 1..64")
+        if s.decay_rank <= 0 or s.gate_rank <= 0:
+            raise ValueError("the low-rank maps of the decay and of the gate need a positive rank")
+        self.hidden_size = hidden_size
+        self.H, self.KH, self.dk, self.dv, self.taps = s.num_heads, s.num_kv_heads, s.key_dim, s.value_dim, s.conv_taps
+        self.qk_cols, self.v_cols = self.KH * self.dk, self.H * self.dv
+        self.conv_cols = 2 * self.qk_cols + self.v_cols
+        # columns of the stacked product: q | k | v | decay map input | gate map input | beta logits
+        self.a1_at = self.conv_cols
+        self.g1_at = self.a1_at + s.decay_rank
+        self.b_at = self.g1_at + s.gate_rank
+        self.in_cols = self.b_at + self.H
+        self.state_numbers = self.H * self.dk * self.dv
+        self.conv_state_at = self.state_numbers
+
+    def param_specs(self):
+        d, s = self.hidden_size, self.spec
+        return {
+            "w_in": ParamSpec((self.in_cols, d), pieces=(self.qk_cols, self.qk_cols, self.v_cols, s.decay_rank, s.gate_rank, self.H)),
+            "conv": ParamSpec((self.conv_cols, self.taps), role="gain", pieces=(self.qk_cols, self.qk_cols, self.v_cols)),
+            "w_a2": ParamSpec((self.H * self.dk, s.decay_rank)),
+            "w_g2": ParamSpec((self.v_cols, s.gate_rank)),
+            "dt_bias": ParamSpec((self.H * self.dk,), role="gain"),
+            "a_log": ParamSpec((self.H,), role="gain"),
+            "out_norm": ParamSpec((self.dv,), role="gain"),
+            "wo": ParamSpec((d, self.v_cols)),
+        }
+
+    def cache_spec(self):
+        """One float32 row per request: S [heads, key_dim, value_dim], then the convolutions' last taps - 1 inputs
+        [taps - 1, q | k | v channels]."""
+        return StateSpec((self.state_numbers + (self.taps - 1) * self.conv_cols,), torch.float32)
+
+    def forward(self, ctx, h, residual, cache, writes_cache: bool) -> None:
+        n = h.shape[0]
+        s = self.spec
+        f32 = torch.float32
+        ld = -(-self.in_cols // 4) * 4                      # rows of the float32 buffers start 16-byte aligned
+        proj = ctx.scratch("delta_proj", (n, ld), f32)[:, :self.in_cols]
+        linear(ctx, h, self.params["w_in"], proj)
+        decay = ctx.scratch("delta_decay", (n, self.H * self.dk), f32)
+        gate = ctx.scratch("delta_gate", (n, self.v_cols), f32)
+        linear(ctx, proj[:, self.a1_at:self.a1_at + s.decay_rank], self.params["w_a2"], decay)
+        linear(ctx, proj[:, self.g1_at:self.g1_at + s.gate_rank], self.params["w_g2"], gate)
+        qkv = ctx.scratch("delta_qkv", (n, self.conv_cols), f32)
+        state = cache.state
+        kernels.short_conv(proj[:, :self.conv_cols], self.params["conv"], qkv, state, self.conv_state_at, ctx.row_seq,
+                           ctx.positions, ctx.seq_first_row, ctx.seq_start_pos, ctx.seq_slots, writes_cache, ctx.status)
+        o = ctx.scratch("delta_o", (n, self.v_cols), f32)
+        kernels.channel_delta(qkv, proj[:, self.b_at:self.b_at + self.H], decay, self.params["dt_bias"], self.params["a_log"],
+                              state, o, ctx.seq_first_row, ctx.seq_start_pos, ctx.seq_slots, self.H, self.KH, self.dk,
+                              self.dv, writes_cache, ctx.status)
+        att = ctx.scratch("att", (n, self.v_cols))
+        kernels.gated_head_norm(o, gate, self.params["out_norm"], att, self.H, s.norm_eps)
+        linear(ctx, att, self.params["wo"], residual, accumulate=not getattr(ctx, "overwrite_output", False))
+
+
+register_part("mixer", "channel_delta", ChannelDelta, replace=True)

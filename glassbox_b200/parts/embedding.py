@@ -40,5 +40,23 @@ class LmHead(OutputHead):
         linear(ctx, hs, self.params["weight"], logits)
 
 
+class ScaledEmbedding(Embedding):
+    """x[i, :] = E[token_i, :] * scale, the product in float32."""
+
+    def forward(self, ctx, tokens, x) -> None:
+        kernels.embed(self.params["weight"], tokens, x, ctx.status, scale=self.spec.scale)
+
+
+class ScaledLmHead(LmHead):
+    """logits = (hs H^T) * scale, the factor applied to the float32 sums."""
+
+    def forward(self, ctx, hs, logits) -> None:
+        linear(ctx, hs, self.params["weight"], logits)
+        if self.spec.scale != 1.0:
+            kernels.scale_(logits, self.spec.scale)
+
+
 register_part("embedding", "embedding", Embedding, replace=True)
+register_part("embedding", "scaled_embedding", ScaledEmbedding, replace=True)
+register_part("head", "scaled_lm_head", ScaledLmHead, replace=True)
 register_part("head", "lm_head", LmHead, replace=True)

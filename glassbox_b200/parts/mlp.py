@@ -32,4 +32,29 @@ class SwiGlu(FeedForward):
         linear(ctx, act, self.params["w_down"], residual, accumulate=True)
 
 
+class SquaredRelu(FeedForward):
+    """Dense feed-forward without a gate: residual += (relu(h Wup^T))^2 Wdown^T, no bias."""
+    accepts_deferred_input = True
+    launches_through_kernels_only = True
+    can_overwrite_output = True
+
+    def __init__(self, spec, *, hidden_size: int):
+        super().__init__(spec)
+        self.hidden_size = hidden_size
+        self.inter = spec.intermediate_size
+
+    def param_specs(self):
+        d, i = self.hidden_size, self.inter
+        return {"w_up": ParamSpec((i, d)), "w_down": ParamSpec((d, i))}
+
+    def forward(self, ctx, h, residual) -> None:
+        n = h.shape[0]
+        up = ctx.scratch("ffn_up", (n, self.inter))
+        act = ctx.scratch("act", (n, self.inter))
+        linear(ctx, h, self.params["w_up"], up)
+        kernels.relu2(up, act)
+        linear(ctx, act, self.params["w_down"], residual, accumulate=not getattr(ctx, "overwrite_output", False))
+
+
 register_part("ffn", "swiglu", SwiGlu, replace=True)
+register_part("ffn", "relu2", SquaredRelu, replace=True)

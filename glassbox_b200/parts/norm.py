@@ -24,5 +24,19 @@ class RmsNorm(Norm):
     def as_rms(self):
         return self.params["weight"], self.eps
 
+    def add_normed(self, ctx, y, x) -> None:
+        kernels.rmsnorm_add(y, self.params["weight"], x, self.eps)
+
+
+class UnitOffsetRmsNorm(RmsNorm):
+    """RMSNorm whose weight is stored around zero: out_j = (1 + w_j) * (x_j / sqrt(mean(x^2) + eps)). The gain 1 + w is
+    formed once, in float32, when the weights arrive; from then on this is an RMSNorm with that gain, and everything
+    that folds or fuses an RMSNorm takes it as one."""
+
+    def bind(self, params) -> None:
+        super().bind(params)
+        self.params["weight"] = (self.params["weight"].float() + 1.0).contiguous()
+
 
 register_part("norm", "rmsnorm", RmsNorm, replace=True)
+register_part("norm", "rmsnorm_unit_offset", UnitOffsetRmsNorm, replace=True)

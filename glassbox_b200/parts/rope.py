@@ -26,19 +26,38 @@ def rotary_table(theta: float, rotary_dim: int, max_position: int) -> torch.Tens
     return torch.from_numpy(np.ascontiguousarray(table))
 
 
+def inverse_frequencies(theta: float, rotary_dim: int) -> torch.Tensor:
+    """float32 [rotary_dim/2]: theta^(-2i / rotary_dim), formed in float64 and rounded once."""
+    i = np.arange(rotary_dim // 2, dtype=np.float64)
+    return torch.from_numpy(np.power(np.float64(theta), -2.0 * i / np.float64(rotary_dim)).astype(np.float32))
+
+
 class Rope(Position):
+    """``pairing`` "half": a (cos, sin) table for the kernels that rotate channel i with channel i + rotary_dim/2.
+    ``pairing`` "interleaved" (channel 2i with 2i + 1): no table; the mixers that take it ask for ``inv_freq`` and
+    form the angle float32(position) * inv_freq[i] and its sine and cosine on the device, so no largest position has to
+    be known beforehand."""
     launches_through_kernels_only = True
 
     def __init__(self, spec, **_):
         super().__init__(spec)
-        if spec.pairing != "half":
-            raise ValueError(f"rope pairing {spec.pairing!r} is not supported (only 'half')")
+        if spec.pairing not in ("half", "interleaved"):
+            raise ValueError(f"rope pairing {spec.pairing!r} is not supported ('half' or 'interleaved')")
         if spec.rotary_dim % 2:
             raise ValueError(f"rotary_dim {spec.rotary_dim} must be even")
         self.rotary_dim = spec.rotary_dim
+        self.pairing = spec.pairing
         self._tables = {}
 
+    def inv_freq(self, device):
+        key = ("inv_freq", str(device))
+        if key not in self._tables:
+            self._tables[key] = inverse_frequencies(self.spec.theta, self.spec.rotary_dim).to(device)
+        return self._tables[key]
+
     def fused_table(self, device):
+        if self.pairing != "half":
+            return None
         key = str(device)
         if key not in self._tables:
             self._tables[key] = rotary_table(self.spec.theta, self.spec.rotary_dim, self.spec.max_position).to(device)
