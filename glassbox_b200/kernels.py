@@ -81,6 +81,9 @@ _SIGNATURES = {
     "gb_gated_head_norm": [_P, _P, _LL, _P, _P, _I, _I, _I, _I, _F, _P],
     "gb_latent_kv_write": [_P, _LL, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
     "gb_latent_attention_rows": [_P, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
+    "gb_latent_attention_mma_supported": [_I, _I, _I],
+    "gb_latent_attention_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _I,
+                                _P, _P],
     "gb_short_conv": [_P, _LL, _P, _P, _LL, _P, _LL, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "gb_channel_delta": [_P, _LL, _P, _LL, _P, _LL, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "gb_program_op_bytes": [],
@@ -884,6 +887,45 @@ def latent_attention_rows(q: torch.Tensor, out: torch.Tensor, cache: torch.Tenso
     _call("gb_latent_attention_rows", _ptr(q), _ptr(out), _dt(q), _ptr(cache), _ptr(block_tables), block_tables.shape[1],
           _ptr(row_seq), _ptr(positions), _ptr(sink), n, heads, c, r, page_size, num_pages, float(scale),
           int(window) if window else 0, _ptr(status), _stream())
+
+
+def latent_attention_mma_supported(dtype: torch.dtype, c: int, r: int, page_size: int) -> bool:
+    """Whether the tensor-core kernel takes this latent size, rotated size and page size (bfloat16 only)."""
+    return dtype == torch.bfloat16 and bool(lib().gb_latent_attention_mma_supported(c, r, page_size))
+
+
+def latent_decode_splits(num_seqs: int, heads: int, max_context: int, target_blocks: int = 148 * 2) -> int:
+    """Into how many shares the keys of a decoded row are cut, so that a small batch still fills the GPU: blocks are
+    (share, group of 16 heads, request); a share is at least one tile of 64 keys."""
+    blocks = max(num_seqs, 1) * -(-heads // 16)
+    tiles = max(1, -(-max_context // 64))
+    return max(1, min(tiles, -(-target_blocks // blocks), 64))
+
+
+def latent_attention_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor,
+                         seq_first_row: torch.Tensor, seq_start_pos: torch.Tensor, positions: torch.Tensor,
+                         sink: Optional[torch.Tensor], heads: int, c: int, r: int, page_size: int, scale: float,
+                         window: Optional[int], status: torch.Tensor, *, max_rows_per_seq: int = 0, decode: bool = False,
+                         splits: int = 1, part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None) -> None:
+    """As ``latent_attention_rows`` on the tensor cores, heads packed into the tiles' rows. ``decode``: every request of the
+    step brings one row (row i is request i) and its keys are cut into ``splits`` shares (``part_o`` float32
+    [n, heads * splits * c] and ``part_ml`` [n, heads * splits * 2] when more than one); otherwise the step's requests
+    bring runs of rows, none longer than ``max_rows_per_seq``."""
+    _cuda(q, out, cache, block_tables, seq_first_row, seq_start_pos, positions, sink, status, part_o, part_ml)
+    n = q.shape[0]
+    assert q.dtype == out.dtype == cache.dtype == torch.bfloat16 and q.is_contiguous() and out.is_contiguous() and cache.is_contiguous()
+    assert q.numel() == n * heads * (c + r) and out.numel() == n * heads * c and cache.shape[-1] == c + r
+    S = seq_start_pos.shape[0]
+    if decode:
+        assert S == n
+        if splits > 1:
+            assert part_o.dtype == part_ml.dtype == torch.float32 and part_o.numel() >= n * heads * splits * c
+            assert part_ml.numel() >= n * heads * splits * 2
+    num_pages = cache.numel() // ((c + r) * page_size)
+    _call("gb_latent_attention_mma", _ptr(q), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(cache), _ptr(block_tables),
+          block_tables.shape[1], _ptr(seq_first_row), _ptr(seq_start_pos), _ptr(positions), _ptr(sink), n, S,
+          int(max_rows_per_seq), heads, c, r, page_size, num_pages, float(scale), int(window) if window else 0,
+          1 if decode else 0, int(splits), _ptr(status), _stream())
 
 
 # ------------------------------------------------------------------------------------- recurrent state mixers

@@ -103,6 +103,25 @@ class LatentAttention(Mixer):
         linear(ctx, att, self.params["wo"], residual, accumulate=not getattr(ctx, "overwrite_output", False))
 
     def attend(self, ctx, qabs, lat, cache) -> None:
+        """lat[row, head, :] = the softmax-weighted sum of the latents the row sees. bfloat16 at the sizes the
+        tensor-core kernel is built for: decode steps cut each row's keys into shares so that few requests still fill the
+        GPU; steps with prompt portions run tiles of tokens x heads. Anything else: one warp per (row, head)."""
+        n = qabs.shape[0]
+        if kernels.latent_attention_mma_supported(qabs.dtype, self.c, self.r, cache.page_size):
+            common = (qabs, lat, cache.k, cache.block_tables, ctx.seq_first_row, ctx.seq_start_pos, ctx.positions,
+                      self.params.get("sink"), self.H, self.c, self.r, cache.page_size, self.spec.scale, self.spec.window,
+                      ctx.status)
+            if ctx.decode_only:
+                window = self.spec.window or ctx.max_context
+                splits = kernels.latent_decode_splits(n, self.H, min(ctx.max_context, window))
+                part_o = part_ml = None
+                if splits > 1:
+                    part_o = ctx.scratch("latent_part_o", (n, self.H * splits * self.c), torch.float32, grow=True)
+                    part_ml = ctx.scratch("latent_part_ml", (n, self.H * splits * 2), torch.float32, grow=True)
+                kernels.latent_attention_mma(*common, decode=True, splits=splits, part_o=part_o, part_ml=part_ml)
+            else:
+                kernels.latent_attention_mma(*common, max_rows_per_seq=ctx.max_rows_per_seq)
+            return
         kernels.latent_attention_rows(qabs, lat, cache.k, cache.block_tables, ctx.row_seq, ctx.positions,
                                       self.params.get("sink"), self.H, self.c, self.r, cache.page_size, self.spec.scale,
                                       self.spec.window, ctx.status)
