@@ -125,20 +125,28 @@ def mean_sd(xs):
 class ModelBench:
     """One SmolLM2 size with random weights in an engine, and the timed regions on it."""
 
-    def __init__(self, model: str, dtype: str, max_batch: int, ctx: int, layers: int = 0, seed: int = 0):
+    def __init__(self, model: str, dtype: str, max_batch: int, ctx: int, layers: int = 0, seed: int = 0, raw: dict = None,
+                 shape: dict = None):
+        """``model`` names one of SHAPES; ``shape`` gives Llama sizes directly instead; ``raw`` gives a whole raw
+        config.json of any registered architecture (``model`` is then only a label)."""
         import numpy as np
         import torch
         import glassbox_b200
         from glassbox_b200.engine.engine import Engine
         from glassbox_b200.models.llama import make_llama_raw_config
         self.model, self.dtype, self.ctx = model, dtype, ctx
-        self.shape = dict(SHAPES[model])
-        self.full_layers = self.shape["num_hidden_layers"]
-        if layers:
-            self.shape["num_hidden_layers"] = min(layers, self.full_layers)
         self.tmp = tempfile.mkdtemp(prefix="glassbox_b200_bench_")
         store = torch.bfloat16 if dtype == "bfloat16" else torch.float32
-        glassbox_b200.write_random_model(self.tmp, make_llama_raw_config(**self.shape), seed=seed, store_dtype=store)
+        if raw is not None:
+            self.shape = {"vocab_size": raw["vocab"] if "vocab" in raw else raw["vocab_size"]}
+            self.full_layers = len(raw["layers"]) if "layers" in raw else raw.get("num_hidden_layers", 0)
+            glassbox_b200.write_random_model(self.tmp, raw, seed=seed, store_dtype=store)
+        else:
+            self.shape = dict(shape if shape is not None else SHAPES[model])
+            self.full_layers = self.shape["num_hidden_layers"]
+            if layers:
+                self.shape["num_hidden_layers"] = min(layers, self.full_layers)
+            glassbox_b200.write_random_model(self.tmp, make_llama_raw_config(**self.shape), seed=seed, store_dtype=store)
         self.page = 16
         self.eng = Engine(self.tmp, dtype, cache_tokens=max_batch * (ctx + self.page) + 4096, page_size=self.page,
                           max_batch_tokens=2048, max_requests=max_batch + 2)
@@ -349,6 +357,65 @@ def serving_workload(args):
         torch.cuda.empty_cache()
 
 
+# ------------------------------------------------------------------------------------------------ Zurerax beside Llama
+#: layer sizes that resemble real models' (random weights): a Zurerax model of three delta-rule layers to one
+#: latent-attention layer, beside the dense Llama decoder of the same width, depth and feed-forward width
+ZURERAX_SIZES = {
+    "w1024": dict(width=1024, ff=4096, layers=8, vocab=32768,
+                  delta=dict(heads=8, kv_heads=8, dim=128, vdim=128, conv=4, decay_rank=64, gate_rank=64),
+                  latent=dict(heads=16, dim=64, rot_dim=32, vdim=64, kv_rank=128),
+                  llama=dict(num_attention_heads=16, num_key_value_heads=4)),
+    "w2048": dict(width=2048, ff=8192, layers=8, vocab=32768,
+                  delta=dict(heads=16, kv_heads=16, dim=128, vdim=128, conv=4, decay_rank=128, gate_rank=128),
+                  latent=dict(heads=32, dim=64, rot_dim=64, vdim=64, kv_rank=128),
+                  llama=dict(num_attention_heads=32, num_key_value_heads=8)),
+}
+
+
+def zurerax_raw(size: dict) -> dict:
+    from glassbox_b200.models.zurerax import make_zurerax_raw_config
+    layers = []
+    for i in range(size["layers"]):
+        mlp = {"kind": "dense", "ff": size["ff"]}
+        if i % 4 == 3:
+            m = dict(size["latent"])
+            m.update(rot={"base": 10000.0, "dims": m["rot_dim"]}, scale=(m["dim"] + m["rot_dim"]) ** -0.5)
+            layers.append({"type": "latent_attention", "mixer": m, "mlp": mlp})
+        else:
+            layers.append({"type": "channel_delta", "mixer": dict(size["delta"]), "mlp": mlp})
+    return make_zurerax_raw_config(vocab=size["vocab"], width=size["width"], layers=layers, embedding_scale=size["width"] ** 0.5,
+                                   logit_scale=1.0)
+
+
+def zurerax_workload(args):
+    """Prefill and decode throughput of Zurerax models beside the Llama decoder of equal width, depth and feed-forward
+    width; one JSON line. Decode steps end at the context length; three timed regions per point."""
+    T, ctx, K, W = 2048, args.context, min(args.steps, 128), max(args.warmup, 3)
+    out = {"workload": "zurerax", "dtype": args.dtype, "context": ctx, "prefill_tokens": T, "decode_steps": K, "sizes": {}}
+    for name, size in ZURERAX_SIZES.items():
+        row = {}
+        llama = dict(num_hidden_layers=size["layers"], hidden_size=size["width"], intermediate_size=size["ff"],
+                     vocab_size=size["vocab"], rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
+                     max_position_embeddings=8192, **size["llama"])
+        for label, kw in (("zurerax", dict(raw=zurerax_raw(size))), ("llama", dict(shape=llama))):
+            mb = ModelBench(f"{label}-{name}", args.dtype, 64, ctx, **kw)
+            try:
+                r = {"weight_mb": round(mb.eng.weight_bytes() / 2 ** 20, 1), "cache_bytes_per_token": mb.eng.cache_bytes_per_token()}
+                times = mb.prefill(T)
+                m, sd = mean_sd(times)
+                r["prefill"] = {"ms": round(m, 3), "sd": round(sd, 3), "tokens_per_s": round(T / (m / 1e3))}
+                for b in (1, 8, 64):
+                    regions, launches, _ = mb.decode(b, K, W, reps=3)
+                    m, sd = mean_sd(regions)
+                    r[f"decode_b{b}"] = {"ms_per_step": round(m / K, 4), "sd": round(sd / K, 4), "tokens_per_s": round(b * K / (m / 1e3)),
+                                         "launches_per_step": round(launches / K, 1)}
+                row[label] = r
+            finally:
+                mb.close()
+        out["sizes"][name] = row
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -363,10 +430,11 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="only the headline region: no other batches, prefill or e2e")
     ap.add_argument("--no-others", action="store_true",
                     help="skip the other model sizes, the serving workload, the 32-bit path and the CPU baseline")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "zurerax"],
                     help="serving: the mixed workload of the 360M configuration (64 requests, prompts 32-2048, outputs "
                          "32-512, prompt portions of 512, a quarter of the requests sharing a 384-token prefix) through "
-                         "the scheduler; prints its own JSON line")
+                         "the scheduler; prints its own JSON line. zurerax: prefill and decode throughput of Zurerax models "
+                         "at two widths beside the Llama decoder of equal size; prints its own JSON line")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -381,6 +449,9 @@ def main():
     import torch  # noqa: F401
     if args.workload == "serving":
         print(json.dumps(serving_workload(args)))
+        return 0
+    if args.workload == "zurerax":
+        print(json.dumps(zurerax_workload(args)))
         return 0
     K, W, B, CTX = args.steps, max(args.warmup, 3), args.batch, args.context
     pk = peaks()

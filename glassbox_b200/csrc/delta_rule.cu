@@ -87,12 +87,20 @@ GB_EXPORT int gb_short_conv(const float* x, long long ldx, const float* w, float
 }
 
 // ----------------------------------------------------------------------------------------------
-// The recurrence. Grid (sequences of the step, heads, column blocks); 128 threads. A thread owns DPT rows of one
-// column of S in registers: lane = column * NS + split, so the NS splits of a column are neighbouring lanes and the
-// two reductions over the key dimension are shuffles. Tokens are staged TC at a time in shared memory (q and k made
-// unit vectors, decays and beta evaluated) by all threads; the walk over the TC tokens needs no block barrier.
+// The recurrence. Grid (sequences of the step, heads, column blocks); 256 threads in two groups of four warps.
+//
+// Walkers: a thread owns DPT rows of one column of S in registers: lane = column * NS + split, so the NS splits of a
+// column are neighbouring lanes and the two reductions over the key dimension are shuffles. Per token the chain that
+// cannot be shortened is: decay, dot with k, reduce, u, update; the read-out's own reduction is put off by one token
+// and rides in the same shuffle rounds as the next token's dot product.
+// Stagers: meanwhile the other four warps prepare the next TC tokens in the second shared-memory buffer: every load
+// of a batch is asked for before the first is used (instructions issue in order: a loop that uses each value as it
+// arrives pays the trip to memory once per round), decays are evaluated (exp(-r * softplus(z)) = exp(-r * log(1 + e^z))
+// with the hardware's exponential and logarithm, whose absolute error of about 1e-7 in the exponent is far below the
+// float32 rounding of the state), then one warp per token sums the squares of q and k. The unit vectors are never
+// formed: 1/|q| and 1/|k| are two numbers per token that the walkers apply to their sums.
 // ----------------------------------------------------------------------------------------------
-constexpr int CD_THREADS = 128;
+constexpr int CD_GROUP = 128, CD_THREADS = 256;
 constexpr float CD_UNIT_EPS = 1e-6f;
 
 struct ChannelDeltaArgs {
@@ -128,112 +136,158 @@ __global__ void __launch_bounds__(CD_THREADS) channel_delta_kernel(ChannelDeltaA
     }
     const int r0 = p.seq_first_row[seq], r1 = p.seq_first_row[seq + 1];
     const int NS = p.ns, TC = p.tc, dk = p.dk, dv = p.dv;
-    const int cols = CD_THREADS / NS;                     // columns of S per block
-    const int split = threadIdx.x % NS, col_local = threadIdx.x / NS;
-    const int col = blockIdx.z * cols + col_local;
-    const bool live = col < dv;
+    const int cols = CD_GROUP / NS;                        // columns of S per block
+    const bool walker = threadIdx.x < CD_GROUP;
+    const int wt = threadIdx.x & (CD_GROUP - 1);           // index within the group
     const int kvh = head / (p.heads / p.kv_heads);
-    constexpr int PAD = DPT + 4;                          // a split's numbers start 16-byte aligned, on other banks than its neighbours'
-    const int row_w = NS * PAD;
-    float* qs = cd_smem;                                  // [TC][row_w]
-    float* ks = qs + (size_t)TC * row_w;
-    float* gs = ks + (size_t)TC * row_w;
-    float* vs = gs + (size_t)TC * row_w;                  // [TC][cols]
-    float* bs = vs + (size_t)TC * cols;                   // [TC]
-
-    float S[DPT];
-    float* sbase = p.state + (size_t)slot * p.state_stride + (size_t)head * dk * dv;
-#pragma unroll
-    for (int i = 0; i < DPT; ++i) {
-        const int d = split * DPT + i;
-        S[i] = (live && d < dk) ? sbase[(size_t)d * dv + col] : 0.f;
-    }
+    constexpr int PAD = DPT + 4;                           // a split's numbers start 16-byte aligned, on other banks than its neighbours'
+    const int row_w = NS * PAD, Dp = NS * DPT;             // Dp: the key size rounded up (a power of two)
+    const int per_token = 3 * row_w + cols + 4;
+    const int buf_floats = TC * per_token;
+    // one buffer: q [TC][row_w], k [TC][row_w], g [TC][row_w], v [TC][cols], scalars [TC][4] = (beta, 1/|q| / sqrt(dk), 1/|k|, -)
+    const int n_chunks = (r1 - r0 + TC - 1) / TC;
     const float decay_rate = expf(p.a_log[head]);
     const float q_scale = 1.0f / sqrtf((float)dk);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    for (int c0 = r0; c0 < r1; c0 += TC) {
+    auto stage = [&](int chunk) {
+        float* buf = cd_smem + (size_t)(chunk & 1) * buf_floats;
+        float* qs = buf, *ks = qs + (size_t)TC * row_w, *gs = ks + (size_t)TC * row_w, *vs = gs + (size_t)TC * row_w;
+        float* sc = vs + (size_t)TC * cols;
+        const int c0 = r0 + chunk * TC;
         const int nt = min(TC, r1 - c0);
-        __syncthreads();       // the walk over the chunk before is done with the staged numbers
-        // staging: a warp per token
-        for (int t = warp; t < nt; t += CD_THREADS / 32) {
-            const size_t row = (size_t)(c0 + t);
-            const float* qrow = p.qkv + row * p.ldq + (size_t)kvh * dk;
-            const float* krow = p.qkv + row * p.ldq + (size_t)(p.kv_heads + kvh) * dk;
-            const float* arow = p.a + row * p.lda + (size_t)head * dk;
-            float sq = 0.f, sk = 0.f;
-            for (int d = lane; d < dk; d += 32) {
-                const float qv = qrow[d], kv = krow[d];
-                sq = fmaf(qv, qv, sq);
-                sk = fmaf(kv, kv, sk);
-            }
-            sq = gb_warp_sum(sq);
-            sk = gb_warp_sum(sk);
-            const float iq = q_scale / sqrtf(sq + CD_UNIT_EPS), ik = 1.0f / sqrtf(sk + CD_UNIT_EPS);
-            for (int d = lane; d < NS * DPT; d += 32) {
-                const int at = t * row_w + (d / DPT) * PAD + d % DPT;
-                if (d < dk) {
-                    const float z = arow[d] + p.dt_bias[(size_t)head * dk + d];
-                    const float sp = z > 20.f ? z : log1pf(expf(z));
-                    qs[at] = qrow[d] * iq;
-                    ks[at] = krow[d] * ik;
-                    gs[at] = expf(-decay_rate * sp);
-                } else {
-                    qs[at] = 0.f;
-                    ks[at] = 0.f;
-                    gs[at] = 1.f;
+        const int total = nt * Dp;
+        for (int base = wt; base < total; base += CD_GROUP * 4) {
+            float qv[4], kv[4], zv[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int idx = base + u * CD_GROUP;
+                const int t = idx / Dp, d = idx % Dp;
+                qv[u] = kv[u] = 0.f;
+                zv[u] = -1e30f;
+                if (idx < total && d < dk) {
+                    const size_t row = (size_t)(c0 + t);
+                    qv[u] = p.qkv[row * p.ldq + (size_t)kvh * dk + d];
+                    kv[u] = p.qkv[row * p.ldq + (size_t)(p.kv_heads + kvh) * dk + d];
+                    zv[u] = p.a[row * p.lda + (size_t)head * dk + d] + p.dt_bias[(size_t)head * dk + d];
                 }
             }
-            if (lane == 0) bs[t] = 1.0f / (1.0f + expf(-p.beta[row * p.ldb + head]));
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int idx = base + u * CD_GROUP;
+                if (idx < total) {
+                    const int t = idx / Dp, d = idx % Dp;
+                    const int at = t * row_w + (d / DPT) * PAD + d % DPT;
+                    const float sp = zv[u] > 15.f ? zv[u] : __logf(1.0f + __expf(zv[u]));     // (padding channels: sp = 0, g = 1)
+                    qs[at] = qv[u];
+                    ks[at] = kv[u];
+                    gs[at] = __expf(-decay_rate * sp);
+                }
+            }
         }
-        for (int idx = threadIdx.x; idx < nt * cols; idx += CD_THREADS) {
+        for (int idx = wt; idx < nt * cols; idx += CD_GROUP) {
             const int t = idx / cols, cl = idx % cols;
             const int cc = blockIdx.z * cols + cl;
             vs[t * cols + cl] = cc < dv ? p.qkv[(size_t)(c0 + t) * p.ldq + (size_t)2 * p.kv_heads * dk + (size_t)head * dv + cc] : 0.f;
         }
-        __syncthreads();
-        for (int t = 0; t < nt; ++t) {
-            const float4* g4 = reinterpret_cast<const float4*>(gs + t * row_w + split * PAD);
-            const float4* k4 = reinterpret_cast<const float4*>(ks + t * row_w + split * PAD);
-            const float4* q4 = reinterpret_cast<const float4*>(qs + t * row_w + split * PAD);
-            float kk[DPT];
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll
-            for (int i = 0; i < DPT / 4; ++i) {
-                const float4 g = g4[i], k = k4[i];
-                kk[4 * i] = k.x; kk[4 * i + 1] = k.y; kk[4 * i + 2] = k.z; kk[4 * i + 3] = k.w;
-                S[4 * i] *= g.x; S[4 * i + 1] *= g.y; S[4 * i + 2] *= g.z; S[4 * i + 3] *= g.w;
-                a0 = fmaf(S[4 * i], k.x, a0);
-                a1 = fmaf(S[4 * i + 1], k.y, a1);
-                a2 = fmaf(S[4 * i + 2], k.z, a2);
-                a3 = fmaf(S[4 * i + 3], k.w, a3);
+        if (wt < nt) sc[wt * 4] = 1.0f / (1.0f + __expf(-p.beta[(size_t)(c0 + wt) * p.ldb + head]));
+        asm volatile("bar.sync 1, 128;" ::: "memory");         // the stagers among themselves
+        const int lane = wt & 31;
+        for (int t = wt >> 5; t < nt; t += CD_GROUP / 32) {
+            float sq = 0.f, sk = 0.f;
+            for (int d = lane; d < dk; d += 32) {
+                const int at = t * row_w + (d / DPT) * PAD + d % DPT;
+                sq = fmaf(qs[at], qs[at], sq);
+                sk = fmaf(ks[at], ks[at], sk);
             }
-            float sk = (a0 + a1) + (a2 + a3);
-            for (int o = 1; o < NS; o <<= 1) sk += __shfl_xor_sync(0xffffffffu, sk, o);
-            const float u = bs[t] * (vs[t * cols + col_local] - sk);
-            a0 = a1 = a2 = a3 = 0.f;
-#pragma unroll
-            for (int i = 0; i < DPT / 4; ++i) {
-                const float4 q = q4[i];
-                S[4 * i] = fmaf(kk[4 * i], u, S[4 * i]);
-                S[4 * i + 1] = fmaf(kk[4 * i + 1], u, S[4 * i + 1]);
-                S[4 * i + 2] = fmaf(kk[4 * i + 2], u, S[4 * i + 2]);
-                S[4 * i + 3] = fmaf(kk[4 * i + 3], u, S[4 * i + 3]);
-                a0 = fmaf(S[4 * i], q.x, a0);
-                a1 = fmaf(S[4 * i + 1], q.y, a1);
-                a2 = fmaf(S[4 * i + 2], q.z, a2);
-                a3 = fmaf(S[4 * i + 3], q.w, a3);
+            sq = gb_warp_sum(sq);
+            sk = gb_warp_sum(sk);
+            if (lane == 0) {
+                sc[t * 4 + 1] = q_scale / sqrtf(sq + CD_UNIT_EPS);
+                sc[t * 4 + 2] = 1.0f / sqrtf(sk + CD_UNIT_EPS);
             }
-            float o = (a0 + a1) + (a2 + a3);
-            for (int w = 1; w < NS; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
-            if (split == 0 && live) p.out[(size_t)(c0 + t) * p.heads * dv + (size_t)head * dv + col] = o;
         }
-    }
-    if (p.write_state) {
+    };
+
+    // walkers: their part of S
+    const int split = wt % NS, col_local = wt / NS;
+    const int col = blockIdx.z * cols + col_local;
+    const bool live = walker && col < dv;
+    float S[DPT];
+    float* sbase = p.state + (size_t)slot * p.state_stride + (size_t)head * dk * dv;
+    if (walker) {
 #pragma unroll
         for (int i = 0; i < DPT; ++i) {
             const int d = split * DPT + i;
-            if (live && d < dk) sbase[(size_t)d * dv + col] = S[i];
+            S[i] = (live && d < dk) ? sbase[(size_t)d * dv + col] : 0.f;
+        }
+    }
+    float o_part = 0.f;          // the read-out of the token before, not yet summed over the splits
+    long long o_row = -1;
+
+    if (!walker) stage(0);
+    __syncthreads();
+    for (int chunk = 0; chunk < n_chunks; ++chunk) {
+        if (!walker) {
+            if (chunk + 1 < n_chunks) stage(chunk + 1);
+        } else {
+            const float* buf = cd_smem + (size_t)(chunk & 1) * buf_floats;
+            const float* qs = buf, *ks = qs + (size_t)TC * row_w, *gs = ks + (size_t)TC * row_w, *vs = gs + (size_t)TC * row_w;
+            const float* sc = vs + (size_t)TC * cols;
+            const int c0 = r0 + chunk * TC;
+            const int nt = min(TC, r1 - c0);
+            for (int t = 0; t < nt; ++t) {
+                const float4* g4 = reinterpret_cast<const float4*>(gs + t * row_w + split * PAD);
+                const float4* k4 = reinterpret_cast<const float4*>(ks + t * row_w + split * PAD);
+                const float4* q4 = reinterpret_cast<const float4*>(qs + t * row_w + split * PAD);
+                const float4 scal = *reinterpret_cast<const float4*>(sc + t * 4);      // beta, 1/|q| / sqrt(dk), 1/|k|
+                const float vt = vs[t * cols + col_local];
+                float kk[DPT];
+                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+                for (int i = 0; i < DPT / 4; ++i) {
+                    const float4 g = g4[i], k = k4[i];
+                    kk[4 * i] = k.x; kk[4 * i + 1] = k.y; kk[4 * i + 2] = k.z; kk[4 * i + 3] = k.w;
+                    S[4 * i] *= g.x; S[4 * i + 1] *= g.y; S[4 * i + 2] *= g.z; S[4 * i + 3] *= g.w;
+                    a0 = fmaf(S[4 * i], k.x, a0);
+                    a1 = fmaf(S[4 * i + 1], k.y, a1);
+                    a2 = fmaf(S[4 * i + 2], k.z, a2);
+                    a3 = fmaf(S[4 * i + 3], k.w, a3);
+                }
+                float sk = (a0 + a1) + (a2 + a3);
+                for (int o = 1; o < NS; o <<= 1) {       // this token's dot product and the last token's read-out, together
+                    sk += __shfl_xor_sync(0xffffffffu, sk, o);
+                    o_part += __shfl_xor_sync(0xffffffffu, o_part, o);
+                }
+                if (o_row >= 0 && split == 0 && live) p.out[(size_t)o_row * p.heads * dv + (size_t)head * dv + col] = o_part;
+                const float u = scal.x * (vt - scal.z * sk) * scal.z;     // beta (v - S^T k), times 1/|k| for the update below
+                a0 = a1 = a2 = a3 = 0.f;
+#pragma unroll
+                for (int i = 0; i < DPT / 4; ++i) {
+                    const float4 q = q4[i];
+                    S[4 * i] = fmaf(kk[4 * i], u, S[4 * i]);
+                    S[4 * i + 1] = fmaf(kk[4 * i + 1], u, S[4 * i + 1]);
+                    S[4 * i + 2] = fmaf(kk[4 * i + 2], u, S[4 * i + 2]);
+                    S[4 * i + 3] = fmaf(kk[4 * i + 3], u, S[4 * i + 3]);
+                    a0 = fmaf(S[4 * i], q.x, a0);
+                    a1 = fmaf(S[4 * i + 1], q.y, a1);
+                    a2 = fmaf(S[4 * i + 2], q.z, a2);
+                    a3 = fmaf(S[4 * i + 3], q.w, a3);
+                }
+                o_part = ((a0 + a1) + (a2 + a3)) * scal.y;
+                o_row = c0 + t;
+            }
+        }
+        __syncthreads();
+    }
+    if (walker) {
+        for (int o = 1; o < NS; o <<= 1) o_part += __shfl_xor_sync(0xffffffffu, o_part, o);
+        if (o_row >= 0 && split == 0 && live) p.out[(size_t)o_row * p.heads * dv + (size_t)head * dv + col] = o_part;
+        if (p.write_state) {
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) {
+                const int d = split * DPT + i;
+                if (live && d < dk) sbase[(size_t)d * dv + col] = S[i];
+            }
         }
     }
 }
@@ -249,15 +303,21 @@ GB_EXPORT int gb_channel_delta(const float* qkv, long long ldq, const float* bet
     const int dpt = dk <= 128 ? 16 : 32;
     int ns = 1;
     while (ns * dpt < dk) ns *= 2;
-    const int cols = CD_THREADS / ns;
-    const int per_token = (3 * ns * (dpt + 4) + cols + 1) * (int)sizeof(float);
-    int tc = (40 * 1024) / per_token;
+    const int cols = CD_GROUP / ns;
+    const int per_token = (3 * ns * (dpt + 4) + cols + 4) * (int)sizeof(float);
+    int tc = (64 * 1024) / (2 * per_token);      // two buffers
     if (tc > 16) tc = 16;
     if (tc < 1) tc = 1;
     ChannelDeltaArgs p = {qkv, ldq, beta, ldb, a, lda, dt_bias, a_log, state, state_stride, out, seq_first_row, seq_start_pos,
                           seq_slots, heads, kv_heads, dk, dv, ns, tc, num_slots, write_state, status};
     dim3 grid(S, heads, gb_ceil_div(dv, cols));
-    const size_t smem = (size_t)tc * per_token;
+    const size_t smem = (size_t)2 * tc * per_token;
+    static bool raised = false;
+    if (!raised) {
+        cudaFuncSetAttribute(channel_delta_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaFuncSetAttribute(channel_delta_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        raised = true;
+    }
     if (dpt == 16)
         gb_launch(GB_PDL_ATTENTION, channel_delta_kernel<16>, grid, dim3(CD_THREADS), smem, stream, p);
     else

@@ -199,7 +199,7 @@ static int check_common(const char* who, const void* x, const float* xres, const
 }
 
 // mode: 0 store bfloat16, 1 store float32, 2 add into float32, 3 gated (W = [gate rows; up rows],
-// N = number of gate rows, c = bfloat16 [M, N]). With x == nullptr the float32 rows `xres` are
+// N = number of gate rows, c = bfloat16 [M, N]), 5 store bfloat16(max(sum, 0)^2). With x == nullptr the float32 rows `xres` are
 // RMS-normalised with `gain` and `eps` on the way in. `prefetch` (optional) names a region that the
 // kernel asks the memory system to bring into L2 for a later kernel. pdl != 0 launches with programmatic stream
 // serialisation (the kernel waits for its predecessor itself, after prefetching weights).
@@ -207,7 +207,7 @@ GB_EXPORT int gb_gemm_stream(const void* x, long long ldx, const float* xres, lo
                              const void* w, long long ldw, void* c, long long ldc, int mode, int M, int N, int K,
                              const void* prefetch, long long prefetch_bytes, int pdl, cudaStream_t stream) {
     if (check_common("gb_gemm_stream", x, xres, w, M, N, K, ldx, ldr, ldw)) return 1;
-    GB_REQUIRE(mode >= 0 && mode <= 3, "gb_gemm_stream: unknown mode %d", mode);
+    GB_REQUIRE((mode >= 0 && mode <= 3) || mode == WS_RELU2_BF16, "gb_gemm_stream: unknown mode %d", mode);
     GB_REQUIRE(mode != WS_GLU_BF16 || N % 16 == 0, "gb_gemm_stream: the gated mode needs N to be a multiple of 16");
     GB_REQUIRE(x != nullptr || gain != nullptr, "gb_gemm_stream: normalising needs a gain");
     if (M == 0) return 0;

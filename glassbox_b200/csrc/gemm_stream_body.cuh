@@ -10,7 +10,7 @@
 
 namespace cg = cooperative_groups;
 
-enum { WS_STORE_BF16 = 0, WS_STORE_F32 = 1, WS_ADD_F32 = 2, WS_GLU_BF16 = 3, WS_ROPE_QKV = 4 };
+enum { WS_STORE_BF16 = 0, WS_STORE_F32 = 1, WS_ADD_F32 = 2, WS_GLU_BF16 = 3, WS_ROPE_QKV = 4, WS_RELU2_BF16 = 5 };
 
 constexpr int WS_PAD = 32;             // padding per activation row: row stride = 16 banks mod 32, so the
                                        // 16-byte operand loads of a quarter-warp never collide
@@ -456,6 +456,9 @@ __device__ __forceinline__ void gemm_stream_body(const StreamArgs& a, const int 
             reinterpret_cast<__nv_bfloat16*>(a.C)[(size_t)tok * a.ldc + n] = __float2bfloat16_rn(g);
         } else if (a.mode == WS_STORE_BF16) {
             reinterpret_cast<__nv_bfloat16*>(a.C)[(size_t)tok * a.ldc + n] = __float2bfloat16_rn(v[0]);
+        } else if (a.mode == WS_RELU2_BF16) {       // squared ReLU, from the float32 sum
+            const float g = fmaxf(v[0], 0.f);
+            reinterpret_cast<__nv_bfloat16*>(a.C)[(size_t)tok * a.ldc + n] = __float2bfloat16_rn(g * g);
         } else if (a.mode == WS_STORE_F32) {
             reinterpret_cast<float*>(a.C)[(size_t)tok * a.ldc + n] = v[0];
         } else {

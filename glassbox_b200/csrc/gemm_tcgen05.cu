@@ -25,7 +25,7 @@
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;        // 64 bfloat16 = 128 bytes = one swizzle row
 
-enum { TC_STORE_BF16 = 0, TC_STORE_F32 = 1, TC_ADD_F32 = 2, TC_ROPE_QKV = 3 };
+enum { TC_STORE_BF16 = 0, TC_STORE_F32 = 1, TC_ADD_F32 = 2, TC_ROPE_QKV = 3, TC_RELU2_BF16 = 4 };   // 4: store bfloat16(max(c, 0)^2)
 
 // What the epilogue of a stacked QKV product needs to rotate the heads and write the cache: the
 // (cos, sin) table [max_pos, hd/2], each row's position (negative: a padding row) and cache slot
@@ -321,7 +321,14 @@ __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant
                         r[j] = __float_as_uint(g / (1.0f + __expf(-g)) * (__uint_as_float(u[j]) * inv_rms));
                     }
                 }
-                if (GATED || mode == TC_STORE_BF16) {
+                if (!GATED && mode == TC_RELU2_BF16) {     // squared ReLU, from the float32 sums
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float g = fmaxf(__uint_as_float(r[j]), 0.f);
+                        r[j] = __float_as_uint(g * g);
+                    }
+                }
+                if (GATED || mode == TC_STORE_BF16 || mode == TC_RELU2_BF16) {
                     // a thread's 32 columns are 64 contiguous bytes: store them directly, 16 bytes at a time
                     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(C) + (size_t)row * ldc + col0;
                     if (row < M) {
@@ -528,7 +535,8 @@ GB_EXPORT int gb_gemm_tcgen05(const void* a, const void* w, void* c, int mode, i
     GB_REQUIRE(gb_gemm_tcgen05_supported(a, w, M, N, K, lda, ldw),
                "gb_gemm_tcgen05: operands must be 16-byte aligned with row strides that are multiples of 8 (M=%d N=%d K=%d)",
                M, N, K);
-    GB_REQUIRE(mode >= 0 && mode <= 2 && ldc >= N && status != nullptr, "gb_gemm_tcgen05: bad mode, ldc or status");
+    GB_REQUIRE(((mode >= 0 && mode <= 2) || mode == TC_RELU2_BF16) && ldc >= N && status != nullptr,
+               "gb_gemm_tcgen05: bad mode, ldc or status");
     GB_REQUIRE(norm_gain == nullptr || (mode == TC_ADD_F32 && pre != nullptr && ss_out != nullptr && ldp >= N &&
                                         (uintptr_t)norm_gain % 16 == 0),
                "gb_gemm_tcgen05: a norm is prepared only by a product that adds into float32, into pre and ss_out");

@@ -84,6 +84,8 @@ _SIGNATURES = {
     "gb_latent_attention_mma_supported": [_I, _I, _I],
     "gb_latent_attention_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _I, _I,
                                 _P, _P],
+    "gb_head_linear_supported": [_P, _LL, _LL, _P, _P, _LL, _LL, _I, _I],
+    "gb_head_linear": [_P, _LL, _LL, _P, _P, _LL, _LL, _I, _I, _I, _I, _P],
     "gb_short_conv": [_P, _LL, _P, _P, _LL, _P, _LL, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "gb_channel_delta": [_P, _LL, _P, _LL, _P, _LL, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "gb_program_op_bytes": [],
@@ -427,7 +429,7 @@ def _prefetch_args(t: Optional[torch.Tensor]):
 
 
 def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool = False, gated: bool = False,
-                norm=None, prefetch: Optional[torch.Tensor] = None) -> None:
+                norm=None, prefetch: Optional[torch.Tensor] = None, relu2: bool = False) -> None:
     """c[M, N] (+)= a[M, K] @ w[N, K]^T for M <= 64 on the tensor cores, streaming w once. With
     ``gated``, w is [2I, K] (gate rows, then up rows) and c[M, I] = silu(a gate^T) * (a up^T). With
     ``norm`` = (gain, eps), ``a`` is the float32 residual and is RMS-normalised on the way in.
@@ -439,6 +441,9 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: b
     if gated:
         assert c.dtype == torch.bfloat16 and not accumulate
         mode = 3
+    elif relu2:                      # c = bfloat16(max(a w^T, 0)^2)
+        assert c.dtype == torch.bfloat16 and not accumulate
+        mode = 5
     elif accumulate:
         assert c.dtype == torch.float32
         mode = 2
@@ -523,7 +528,7 @@ def gemm_tc_column_tiles(rows: int, n: int, k: int) -> int:
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool = False,
-            status: Optional[torch.Tensor] = None, prepare=None, row_scale: Optional[RowScale] = None) -> None:
+            status: Optional[torch.Tensor] = None, prepare=None, row_scale: Optional[RowScale] = None, relu2: bool = False) -> None:
     """c[M, N] (+)= a[M, K] @ w[N, K]^T with TMA + tcgen05.mma + TMEM. ``status`` receives the
     wait-timeout bit if a bounded wait inside the kernel ever gives up.
 
@@ -547,7 +552,10 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool 
         status = _tc_status.get(a.device)
         if status is None:
             status = _tc_status[a.device] = torch.zeros(1, dtype=torch.int32, device=a.device)
-    if accumulate:
+    if relu2:                        # c = bfloat16(max(a w^T, 0)^2)
+        assert c.dtype == torch.bfloat16 and not accumulate
+        mode = 4
+    elif accumulate:
         assert c.dtype == torch.float32
         mode = 2
     else:
@@ -887,6 +895,26 @@ def latent_attention_rows(q: torch.Tensor, out: torch.Tensor, cache: torch.Tenso
     _call("gb_latent_attention_rows", _ptr(q), _ptr(out), _dt(q), _ptr(cache), _ptr(block_tables), block_tables.shape[1],
           _ptr(row_seq), _ptr(positions), _ptr(sink), n, heads, c, r, page_size, num_pages, float(scale),
           int(window) if window else 0, _ptr(status), _stream())
+
+
+def head_linear_supported(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, a_head: int, c_head: int) -> bool:
+    """Whether ``head_linear`` takes these operands: bfloat16, a head's input size a multiple of 16 up to 256, aligned."""
+    if not (a.dtype == w.dtype == out.dtype == torch.bfloat16) or w.dim() != 3 or not w.is_contiguous():
+        return False
+    if a.stride(1) != 1 or out.stride(1) != 1:
+        return False
+    return bool(lib().gb_head_linear_supported(_ptr(a), a.stride(0), a_head, _ptr(w), _ptr(out), out.stride(0), c_head,
+                                               w.shape[1], w.shape[2]))
+
+
+def head_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, a_head: int, c_head: int) -> None:
+    """out[row, h * c_head : h * c_head + N] = a[row, h * a_head : h * a_head + K] @ w[h]^T for every head h of
+    w [heads, N, K], in one launch (bfloat16, float32 sums)."""
+    _cuda(a, w, out)
+    heads, N, K = w.shape
+    n = a.shape[0]
+    assert out.shape[0] == n and a.shape[1] >= (heads - 1) * a_head + K and out.shape[1] >= (heads - 1) * c_head + N
+    _call("gb_head_linear", _ptr(a), a.stride(0), a_head, _ptr(w), _ptr(out), out.stride(0), c_head, n, heads, N, K, _stream())
 
 
 def latent_attention_mma_supported(dtype: torch.dtype, c: int, r: int, page_size: int) -> bool:

@@ -69,7 +69,7 @@ class LatentAttention(Mixer):
         # W_uk is applied to the query: per head the [latent_dim, nope_dim] transpose, contiguous, as a product's weight
         w_uk = self.params["w_uk"]
         self.w_uk_t = w_uk.view(self.H, self.dq, self.c).transpose(1, 2).contiguous() if self.dq else None
-        self.w_uv = self.params["w_uv"].view(self.H, self.dv, self.c)
+        self.w_uv = self.params["w_uv"].view(self.H, self.dv, self.c).contiguous()
 
     def cache_spec(self):
         return PagedKvSpec(1, self.c + self.r, self.spec.window, value_dim=0)
@@ -87,19 +87,27 @@ class LatentAttention(Mixer):
                                 self.position.inv_freq(proj.device) if r else proj.new_zeros(1, dtype=torch.float32),
                                 ctx.positions, cache.slots, H, dq, r, c, self.position.rotary_dim if r else 0,
                                 self.spec.latent_eps, writes_cache and self.owns_cache, ctx.status)
-        q3 = qabs.view(n, H, c + r)
-        p3 = proj[:, :self.q_cols].unflatten(1, (H, dq + r))
-        for head in range(H):          # the key up-projection, applied to the query
-            if dq:
-                linear(ctx, p3[:, head, :dq], self.w_uk_t[head], q3[:, head, :c])
-            else:
-                q3[:, head, :c].zero_()
+        # the key up-projection, applied to the query: one launch for all heads where the sizes allow, else head by head
+        if dq and kernels.head_linear_supported(proj, self.w_uk_t, qabs, dq + r, c + r):
+            kernels.head_linear(proj, self.w_uk_t, qabs, dq + r, c + r)
+        else:
+            q3 = qabs.view(n, H, c + r)
+            p3 = proj[:, :self.q_cols].unflatten(1, (H, dq + r))
+            for head in range(H):
+                if dq:
+                    linear(ctx, p3[:, head, :dq], self.w_uk_t[head], q3[:, head, :c])
+                else:
+                    q3[:, head, :c].zero_()
         lat = ctx.scratch("latent_out", (n, H * c))
         self.attend(ctx, qabs, lat, cache)
         att = ctx.scratch("att", (n, H * dv))
-        l3, a3 = lat.view(n, H, c), att.view(n, H, dv)
-        for head in range(H):          # the value up-projection, applied to the weighted sum of latents
-            linear(ctx, l3[:, head, :], self.w_uv[head], a3[:, head, :])
+        # the value up-projection, applied to the weighted sum of latents
+        if kernels.head_linear_supported(lat, self.w_uv, att, c, dv):
+            kernels.head_linear(lat, self.w_uv, att, c, dv)
+        else:
+            l3, a3 = lat.view(n, H, c), att.view(n, H, dv)
+            for head in range(H):
+                linear(ctx, l3[:, head, :], self.w_uv[head], a3[:, head, :])
         linear(ctx, att, self.params["wo"], residual, accumulate=not getattr(ctx, "overwrite_output", False))
 
     def attend(self, ctx, qabs, lat, cache) -> None:

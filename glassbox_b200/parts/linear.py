@@ -115,3 +115,23 @@ def gated_linear(ctx, a, w_gate_up: torch.Tensor, act: torch.Tensor) -> bool:
         kernels.gemm_tc_gated(x, w_gate_up, act, ctx.status)
         return True
     return False
+
+
+def relu2_linear(ctx, a, w: torch.Tensor, act: torch.Tensor) -> bool:
+    """act = max(a w^T, 0)^2 in one kernel (the activation in the product's epilogue, from the float32 sums) when the
+    operands are bfloat16 and a tensor-core kernel takes them; returns False (and does nothing) otherwise."""
+    if w.dtype != torch.bfloat16 or act.dtype != torch.bfloat16:
+        return False
+    x, norm, deferred, scale = _resolve(a, w)
+    if scale is not None:
+        x, scale = deferred.tensor(), None
+    wide = norm is None and _tile_kernel_wins(x.shape[0], w) and kernels.gemm_tc_supported(x, w, act)
+    if not wide and kernels.gemm_stream_supported(x, w) and (norm is not None or x.dtype == torch.bfloat16):
+        kernels.gemm_stream(x, w, act, norm=norm, prefetch=weights_ahead(ctx, w), relu2=True)
+        return True
+    if deferred is not None:
+        x = deferred.tensor()
+    if x.dtype == torch.bfloat16 and kernels.gemm_tc_supported(x, w, act):
+        kernels.gemm_tc(x, w, act, False, ctx.status, relu2=True)
+        return True
+    return False

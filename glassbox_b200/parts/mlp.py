@@ -6,7 +6,7 @@ from __future__ import annotations
 from .. import kernels
 from ..weights.binding import ParamSpec
 from .base import FeedForward, register_part
-from .linear import gated_linear, linear
+from .linear import gated_linear, linear, relu2_linear
 
 
 class SwiGlu(FeedForward):
@@ -49,10 +49,11 @@ class SquaredRelu(FeedForward):
 
     def forward(self, ctx, h, residual) -> None:
         n = h.shape[0]
-        up = ctx.scratch("ffn_up", (n, self.inter))
         act = ctx.scratch("act", (n, self.inter))
-        linear(ctx, h, self.params["w_up"], up)
-        kernels.relu2(up, act)
+        if not relu2_linear(ctx, h, self.params["w_up"], act):
+            up = ctx.scratch("ffn_up", (n, self.inter))
+            linear(ctx, h, self.params["w_up"], up)
+            kernels.relu2(up, act)
         linear(ctx, act, self.params["w_down"], residual, accumulate=not getattr(ctx, "overwrite_output", False))
 
 

@@ -176,6 +176,38 @@ def test_branch_norm_head_norm_activation_and_scales():
     assert torch.equal(emb, table[[4, 0, 10]].float() * 1.75 * -0.5)
 
 
+@pytest.mark.parametrize("n, heads, N, K", [(1, 3, 40, 16), (70, 6, 128, 64), (200, 16, 64, 128), (33, 2, 130, 256)])
+def test_one_small_product_per_head(n, heads, N, K):
+    from glassbox_b200 import kernels
+    g = torch.Generator(device="cpu").manual_seed(n)
+    a_head, c_head = K + 8, N + 6
+    a = torch.randn((n, heads * a_head), generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn((heads, N, K), generator=g) / K ** 0.5).to(torch.bfloat16).to(DEV)
+    out = torch.full((n, heads * c_head), 9.0, dtype=torch.bfloat16, device=DEV)
+    assert kernels.head_linear_supported(a, w, out, a_head, c_head)
+    kernels.head_linear(a, w, out, a_head, c_head)
+    a3 = a.float().view(n, heads, a_head)[:, :, :K]
+    want = torch.einsum("nhk,hck->nhc", a3, w.float())
+    got = out.float().view(n, heads, c_head)
+    assert torch.allclose(got[:, :, :N], want, atol=0.03, rtol=0.02)
+    assert torch.all(got[:, :, N:] == 9.0)                          # columns between the heads' outputs are not touched
+
+
+def test_squared_relu_in_the_products_epilogue():
+    from glassbox_b200 import kernels
+    g = torch.Generator(device="cpu").manual_seed(3)
+    for rows in (5, 200):
+        a = torch.randn((rows, 128), generator=g).to(torch.bfloat16).to(DEV)
+        w = (torch.randn((272, 128), generator=g) / 11).to(torch.bfloat16).to(DEV)
+        want = torch.clamp(a.float() @ w.float().T, min=0) ** 2
+        got = torch.zeros((rows, 272), dtype=torch.bfloat16, device=DEV)
+        if rows <= kernels.STREAM_MAX_ROWS:
+            kernels.gemm_stream(a, w, got, relu2=True)
+        else:
+            kernels.gemm_tc(a, w, got, relu2=True)
+        assert torch.allclose(got.float(), want, atol=0.02, rtol=0.02), rows
+
+
 def _run_latent_kernel(how, q, cache, table, lengths, sink, H, c, r, page):
     """q [n, H, c + r] for n requests that each bring their last token (request i holds ``lengths[i]`` tokens)."""
     from glassbox_b200 import kernels
