@@ -87,20 +87,20 @@ GB_EXPORT int gb_short_conv(const float* x, long long ldx, const float* w, float
 }
 
 // ----------------------------------------------------------------------------------------------
-// The recurrence. Grid (sequences of the step, heads, column blocks); 256 threads in two groups of four warps.
+// The recurrence. Grid (sequences of the step, heads, column blocks); four walking warps and eight staging warps.
 //
 // Walkers: a thread owns DPT rows of one column of S in registers: lane = column * NS + split, so the NS splits of a
 // column are neighbouring lanes and the two reductions over the key dimension are shuffles. Per token the chain that
 // cannot be shortened is: decay, dot with k, reduce, u, update; the read-out's own reduction is put off by one token
 // and rides in the same shuffle rounds as the next token's dot product.
-// Stagers: meanwhile the other four warps prepare the next TC tokens in the second shared-memory buffer: every load
+// Stagers: meanwhile the other eight warps prepare the next TC tokens in the second shared-memory buffer: every load
 // of a batch is asked for before the first is used (instructions issue in order: a loop that uses each value as it
 // arrives pays the trip to memory once per round), decays are evaluated (exp(-r * softplus(z)) = exp(-r * log(1 + e^z))
 // with the hardware's exponential and logarithm, whose absolute error of about 1e-7 in the exponent is far below the
 // float32 rounding of the state), then one warp per token sums the squares of q and k. The unit vectors are never
 // formed: 1/|q| and 1/|k| are two numbers per token that the walkers apply to their sums.
 // ----------------------------------------------------------------------------------------------
-constexpr int CD_GROUP = 128, CD_THREADS = 256;
+constexpr int CD_GROUP = 128, CD_STAGERS = 256, CD_THREADS = CD_GROUP + CD_STAGERS;   // walkers first, then stagers
 constexpr float CD_UNIT_EPS = 1e-6f;
 
 struct ChannelDeltaArgs {
@@ -138,10 +138,11 @@ __global__ void __launch_bounds__(CD_THREADS) channel_delta_kernel(ChannelDeltaA
     const int NS = p.ns, TC = p.tc, dk = p.dk, dv = p.dv;
     const int cols = CD_GROUP / NS;                        // columns of S per block
     const bool walker = threadIdx.x < CD_GROUP;
-    const int wt = threadIdx.x & (CD_GROUP - 1);           // index within the group
+    const int wt = walker ? threadIdx.x : threadIdx.x - CD_GROUP;     // index within the group
     const int kvh = head / (p.heads / p.kv_heads);
     constexpr int PAD = DPT + 4;                           // a split's numbers start 16-byte aligned, on other banks than its neighbours'
     const int row_w = NS * PAD, Dp = NS * DPT;             // Dp: the key size rounded up (a power of two)
+    const int dp_shift = 31 - __clz(Dp), cols_shift = 31 - __clz(cols);
     const int per_token = 3 * row_w + cols + 4;
     const int buf_floats = TC * per_token;
     // one buffer: q [TC][row_w], k [TC][row_w], g [TC][row_w], v [TC][cols], scalars [TC][4] = (beta, 1/|q| / sqrt(dk), 1/|k|, -)
@@ -156,12 +157,19 @@ __global__ void __launch_bounds__(CD_THREADS) channel_delta_kernel(ChannelDeltaA
         const int c0 = r0 + chunk * TC;
         const int nt = min(TC, r1 - c0);
         const int total = nt * Dp;
-        for (int base = wt; base < total; base += CD_GROUP * 4) {
-            float qv[4], kv[4], zv[4];
+        // everything the chunk needs from memory is asked for before anything is used
+        const int vidx = wt, vt_ = vidx >> cols_shift, vcl = vidx & (cols - 1), vcc = blockIdx.z * cols + vcl;
+        float vv = 0.f, bb = 0.f;
+        if (vidx < nt * cols && vcc < dv)
+            vv = p.qkv[(size_t)(c0 + vt_) * p.ldq + (size_t)2 * p.kv_heads * dk + (size_t)head * dv + vcc];
+        if (wt < nt) bb = p.beta[(size_t)(c0 + wt) * p.ldb + head];
+        constexpr int U = 8;
+        for (int base = wt; base < total; base += CD_STAGERS * U) {
+            float qv[U], kv[U], zv[U];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int idx = base + u * CD_GROUP;
-                const int t = idx / Dp, d = idx % Dp;
+            for (int u = 0; u < U; ++u) {
+                const int idx = base + u * CD_STAGERS;
+                const int t = idx >> dp_shift, d = idx & (Dp - 1);
                 qv[u] = kv[u] = 0.f;
                 zv[u] = -1e30f;
                 if (idx < total && d < dk) {
@@ -172,10 +180,10 @@ __global__ void __launch_bounds__(CD_THREADS) channel_delta_kernel(ChannelDeltaA
                 }
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int idx = base + u * CD_GROUP;
+            for (int u = 0; u < U; ++u) {
+                const int idx = base + u * CD_STAGERS;
                 if (idx < total) {
-                    const int t = idx / Dp, d = idx % Dp;
+                    const int t = idx >> dp_shift, d = idx & (Dp - 1);
                     const int at = t * row_w + (d / DPT) * PAD + d % DPT;
                     const float sp = zv[u] > 15.f ? zv[u] : __logf(1.0f + __expf(zv[u]));     // (padding channels: sp = 0, g = 1)
                     qs[at] = qv[u];
@@ -184,15 +192,16 @@ __global__ void __launch_bounds__(CD_THREADS) channel_delta_kernel(ChannelDeltaA
                 }
             }
         }
-        for (int idx = wt; idx < nt * cols; idx += CD_GROUP) {
-            const int t = idx / cols, cl = idx % cols;
+        if (vidx < nt * cols) vs[vidx] = vv;
+        for (int idx = wt + CD_STAGERS; idx < nt * cols; idx += CD_STAGERS) {     // (more than 256 values: few splits, many columns)
+            const int t = idx >> cols_shift, cl = idx & (cols - 1);
             const int cc = blockIdx.z * cols + cl;
-            vs[t * cols + cl] = cc < dv ? p.qkv[(size_t)(c0 + t) * p.ldq + (size_t)2 * p.kv_heads * dk + (size_t)head * dv + cc] : 0.f;
+            vs[idx] = cc < dv ? p.qkv[(size_t)(c0 + t) * p.ldq + (size_t)2 * p.kv_heads * dk + (size_t)head * dv + cc] : 0.f;
         }
-        if (wt < nt) sc[wt * 4] = 1.0f / (1.0f + __expf(-p.beta[(size_t)(c0 + wt) * p.ldb + head]));
-        asm volatile("bar.sync 1, 128;" ::: "memory");         // the stagers among themselves
+        if (wt < nt) sc[wt * 4] = 1.0f / (1.0f + __expf(-bb));
+        asm volatile("bar.sync 1, 256;" ::: "memory");         // the stagers among themselves
         const int lane = wt & 31;
-        for (int t = wt >> 5; t < nt; t += CD_GROUP / 32) {
+        for (int t = wt >> 5; t < nt; t += CD_STAGERS / 32) {
             float sq = 0.f, sk = 0.f;
             for (int d = lane; d < dk; d += 32) {
                 const int at = t * row_w + (d / DPT) * PAD + d % DPT;
@@ -323,4 +332,155 @@ GB_EXPORT int gb_channel_delta(const float* qkv, long long ldq, const float* bet
     else
         gb_launch(GB_PDL_ATTENTION, channel_delta_kernel<32>, grid, dim3(CD_THREADS), smem, stream, p);
     return gb_check_launch("gb_channel_delta");
+}
+
+// ----------------------------------------------------------------------------------------------
+// The same recurrence for steps in which every request brings ONE token (decoding): the work is reading and writing
+// S once, so the layout is chosen for that. One block per (request, head), eight warps; warp w owns rows
+// 16 w .. 16 w + 15 of S and lane l the columns l, l + 32, l + 64, l + 96: every load and store of a warp is a row
+// segment of 128 contiguous bytes, and all 64 loads of a thread are asked for before anything else happens. The two
+// sums over the key dimension cross the warps through shared memory. The read-out's norm and gate are applied here
+// too (the block holds the whole head): the output is the mixer's activation, ready for its output projection.
+// Key and value sizes up to 128.
+// ----------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) channel_delta_decode_kernel(ChannelDeltaArgs p, const float* __restrict__ gate, long long ldg,
+                                                                   const float* __restrict__ norm_w, float eps, T* __restrict__ att) {
+    __shared__ float qs[128], ks[128], gs[128], part[8][128], ovec[128], red[16];
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    const int seq = blockIdx.x, head = blockIdx.y;
+    if (p.seq_start_pos[seq] < 0) return;
+    const int slot = p.seq_slots[seq];
+    if (slot < 0 || slot >= p.num_slots) {
+        if (threadIdx.x == 0) atomicOr(p.status, GB_STATUS_BAD_SLOT);
+        return;
+    }
+    const size_t row = (size_t)p.seq_first_row[seq];
+    const int dk = p.dk, dv = p.dv;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+    const int kvh = head / (p.heads / p.kv_heads);
+    float* sbase = p.state + (size_t)slot * p.state_stride + (size_t)head * dk * dv;
+    float S[16][4];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int d = warp * 16 + i;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int col = lane + 32 * c;
+            S[i][c] = (d < dk && col < dv) ? sbase[(size_t)d * dv + col] : 0.f;
+        }
+    }
+    // the token's vectors: thread d takes key channel d
+    float qv = 0.f, kv = 0.f, zv = -1e30f;
+    if (tid < dk) {
+        qv = p.qkv[row * p.ldq + (size_t)kvh * dk + tid];
+        kv = p.qkv[row * p.ldq + (size_t)(p.kv_heads + kvh) * dk + tid];
+        zv = p.a[row * p.lda + (size_t)head * dk + tid] + p.dt_bias[(size_t)head * dk + tid];
+    }
+    float vt[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const int col = lane + 32 * c;
+        vt[c] = col < dv ? p.qkv[row * p.ldq + (size_t)2 * p.kv_heads * dk + (size_t)head * dv + col] : 0.f;
+    }
+    const float beta = 1.0f / (1.0f + __expf(-p.beta[row * p.ldb + head]));
+    if (tid < 128) {
+        const float sp = zv > 15.f ? zv : __logf(1.0f + __expf(zv));
+        qs[tid] = qv;
+        ks[tid] = kv;
+        gs[tid] = __expf(-expf(p.a_log[head]) * sp);
+        const float sq = gb_warp_sum(qv * qv), sk = gb_warp_sum(kv * kv);
+        if (lane == 0) { red[warp] = sq; red[4 + warp] = sk; }
+    }
+    __syncthreads();
+    const float iq = 1.0f / sqrtf((float)dk) / sqrtf(red[0] + red[1] + red[2] + red[3] + CD_UNIT_EPS);
+    const float ik = 1.0f / sqrtf(red[4] + red[5] + red[6] + red[7] + CD_UNIT_EPS);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float g = gs[warp * 16 + i], k = ks[warp * 16 + i];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            S[i][c] *= g;
+            acc[c] = fmaf(S[i][c], k, acc[c]);
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) part[warp][lane + 32 * c] = acc[c];
+    __syncthreads();
+    float u[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const int col = lane + 32 * c;
+        float sk = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) sk += part[w][col];
+        u[c] = beta * (vt[c] - ik * sk) * ik;
+        acc[c] = 0.f;
+    }
+    __syncthreads();           // everyone has read the first sums before the second ones overwrite them
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float k = ks[warp * 16 + i], q = qs[warp * 16 + i];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            S[i][c] = fmaf(k, u[c], S[i][c]);
+            acc[c] = fmaf(S[i][c], q, acc[c]);
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) part[warp][lane + 32 * c] = acc[c];
+    if (p.write_state) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int d = warp * 16 + i;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int col = lane + 32 * c;
+                if (d < dk && col < dv) sbase[(size_t)d * dv + col] = S[i][c];
+            }
+        }
+    }
+    __syncthreads();
+    if (tid < 128) {
+        float o = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) o += part[w][tid];
+        o = tid < dv ? o * iq : 0.f;
+        ovec[tid] = o;
+        const float ss = gb_warp_sum(o * o);
+        if (lane == 0) red[8 + warp] = ss;
+    }
+    __syncthreads();
+    if (tid < dv) {
+        const float s = 1.0f / sqrtf((red[8] + red[9] + red[10] + red[11]) / (float)dv + eps);
+        const float sig = 1.0f / (1.0f + expf(-gate[row * ldg + (size_t)head * dv + tid]));
+        att[row * p.heads * dv + (size_t)head * dv + tid] = gb_from_float<T>(ovec[tid] * s * norm_w[tid] * sig);
+    }
+}
+
+GB_EXPORT int gb_channel_delta_decode_supported(int dk, int dv) { return dk > 0 && dk <= 128 && dv > 0 && dv <= 128; }
+
+// Every sequence of the step brings exactly one row. att: [n, heads * dv] in `att_dtype`, the gated and normed read-out.
+GB_EXPORT int gb_channel_delta_decode(const float* qkv, long long ldq, const float* beta, long long ldb, const float* a, long long lda,
+                                      const float* dt_bias, const float* a_log, float* state, long long state_stride,
+                                      const float* gate, long long ldg, const float* norm_w, float eps, void* att, int att_dtype,
+                                      const int* seq_first_row, const int* seq_start_pos, const int* seq_slots, int S, int heads,
+                                      int kv_heads, int dk, int dv, int num_slots, int write_state, int* status, cudaStream_t stream) {
+    GB_REQUIRE(S >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "gb_channel_delta_decode: heads %d must be a multiple of "
+               "key heads %d", heads, kv_heads);
+    GB_REQUIRE(gb_channel_delta_decode_supported(dk, dv), "gb_channel_delta_decode: key size %d and value size %d must be at most 128", dk, dv);
+    if (S == 0) return 0;
+    ChannelDeltaArgs p = {qkv, ldq, beta, ldb, a, lda, dt_bias, a_log, state, state_stride, nullptr, seq_first_row, seq_start_pos,
+                          seq_slots, heads, kv_heads, dk, dv, 0, 0, num_slots, write_state, status};
+    dim3 grid(S, heads);
+    if (att_dtype == GB_F32)
+        gb_launch(GB_PDL_ATTENTION, channel_delta_decode_kernel<float>, grid, dim3(256), 0, stream, p, gate, ldg, norm_w, eps, (float*)att);
+    else if (att_dtype == GB_BF16)
+        gb_launch(GB_PDL_ATTENTION, channel_delta_decode_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, p, gate, ldg, norm_w, eps,
+                  (__nv_bfloat16*)att);
+    else
+        GB_REQUIRE(false, "gb_channel_delta_decode: unsupported output dtype %d", att_dtype);
+    return gb_check_launch("gb_channel_delta_decode");
 }

@@ -88,6 +88,9 @@ _SIGNATURES = {
     "gb_head_linear": [_P, _LL, _LL, _P, _P, _LL, _LL, _I, _I, _I, _I, _P],
     "gb_short_conv": [_P, _LL, _P, _P, _LL, _P, _LL, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "gb_channel_delta": [_P, _LL, _P, _LL, _P, _LL, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "gb_channel_delta_decode_supported": [_I, _I],
+    "gb_channel_delta_decode": [_P, _LL, _P, _LL, _P, _LL, _P, _P, _P, _LL, _P, _LL, _P, _F, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I,
+                                _I, _I, _P, _P],
     "gb_program_op_bytes": [],
     "gb_program_max_rows": [],
 }
@@ -993,3 +996,28 @@ def channel_delta(qkv: torch.Tensor, beta: torch.Tensor, a: torch.Tensor, dt_bia
     _call("gb_channel_delta", _ptr(qkv), qkv.stride(0), _ptr(beta), beta.stride(0), _ptr(a), a.stride(0), _ptr(dt_bias),
           _ptr(a_log), _ptr(state), state.stride(0), _ptr(out), _ptr(seq_first_row), _ptr(seq_start_pos), _ptr(seq_slots),
           seq_start_pos.shape[0], heads, kv_heads, dk, dv, state.shape[0], 1 if write_state else 0, _ptr(status), _stream())
+
+
+def channel_delta_decode_supported(dk: int, dv: int) -> bool:
+    return bool(lib().gb_channel_delta_decode_supported(dk, dv))
+
+
+def channel_delta_decode(qkv: torch.Tensor, beta: torch.Tensor, a: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor,
+                         state: torch.Tensor, gate: torch.Tensor, norm_weight: torch.Tensor, eps: float, att: torch.Tensor,
+                         seq_first_row: torch.Tensor, seq_start_pos: torch.Tensor, seq_slots: torch.Tensor, heads: int,
+                         kv_heads: int, dk: int, dv: int, write_state: bool, status: torch.Tensor) -> None:
+    """``channel_delta`` for a step in which every request brings one row, with the read-out's norm and gate applied as
+    well: ``att`` [n, heads * dv] (any activation dtype) = norm_weight * o / rms(o) * sigmoid(gate). Reads and writes
+    each request's S once, in whole rows."""
+    _cuda(qkv, beta, a, dt_bias, a_log, state, gate, norm_weight, att, seq_first_row, seq_start_pos, seq_slots, status)
+    n = qkv.shape[0]
+    for t in (qkv, beta, a, dt_bias, a_log, state, gate, norm_weight):
+        assert t.dtype == torch.float32
+    assert qkv.shape[1] == 2 * kv_heads * dk + heads * dv and qkv.stride(1) == 1 and beta.shape == (n, heads)
+    assert a.shape == (n, heads * dk) and a.stride(1) == 1 and beta.stride(1) == 1 and gate.shape == (n, heads * dv)
+    assert gate.stride(1) == 1 and att.shape == (n, heads * dv) and att.is_contiguous()
+    assert state.dim() == 2 and state.is_contiguous() and state.shape[1] >= heads * dk * dv and norm_weight.numel() == dv
+    _call("gb_channel_delta_decode", _ptr(qkv), qkv.stride(0), _ptr(beta), beta.stride(0), _ptr(a), a.stride(0), _ptr(dt_bias),
+          _ptr(a_log), _ptr(state), state.stride(0), _ptr(gate), gate.stride(0), _ptr(norm_weight), float(eps), _ptr(att),
+          _dt(att), _ptr(seq_first_row), _ptr(seq_start_pos), _ptr(seq_slots), seq_start_pos.shape[0], heads, kv_heads, dk, dv,
+          state.shape[0], 1 if write_state else 0, _ptr(status), _stream())

@@ -85,12 +85,18 @@ class ChannelDelta(Mixer):
         state = cache.state
         kernels.short_conv(proj[:, :self.conv_cols], self.params["conv"], qkv, state, self.conv_state_at, ctx.row_seq,
                            ctx.positions, ctx.seq_first_row, ctx.seq_start_pos, ctx.seq_slots, writes_cache, ctx.status)
-        o = ctx.scratch("delta_o", (n, self.v_cols), f32)
-        kernels.channel_delta(qkv, proj[:, self.b_at:self.b_at + self.H], decay, self.params["dt_bias"], self.params["a_log"],
-                              state, o, ctx.seq_first_row, ctx.seq_start_pos, ctx.seq_slots, self.H, self.KH, self.dk,
-                              self.dv, writes_cache, ctx.status)
         att = ctx.scratch("att", (n, self.v_cols))
-        kernels.gated_head_norm(o, gate, self.params["out_norm"], att, self.H, s.norm_eps)
+        beta = proj[:, self.b_at:self.b_at + self.H]
+        if ctx.decode_only and kernels.channel_delta_decode_supported(self.dk, self.dv):
+            # one token per request: S is read and written once, in whole rows; norm and gate in the same kernel
+            kernels.channel_delta_decode(qkv, beta, decay, self.params["dt_bias"], self.params["a_log"], state, gate,
+                                         self.params["out_norm"], s.norm_eps, att, ctx.seq_first_row, ctx.seq_start_pos,
+                                         ctx.seq_slots, self.H, self.KH, self.dk, self.dv, writes_cache, ctx.status)
+        else:
+            o = ctx.scratch("delta_o", (n, self.v_cols), f32)
+            kernels.channel_delta(qkv, beta, decay, self.params["dt_bias"], self.params["a_log"], state, o, ctx.seq_first_row,
+                                  ctx.seq_start_pos, ctx.seq_slots, self.H, self.KH, self.dk, self.dv, writes_cache, ctx.status)
+            kernels.gated_head_norm(o, gate, self.params["out_norm"], att, self.H, s.norm_eps)
         linear(ctx, att, self.params["wo"], residual, accumulate=not getattr(ctx, "overwrite_output", False))
 
 

@@ -150,6 +150,48 @@ def test_delta_rule_kernel(H, KH, D, V):
     assert torch.all(state[1] == 3.0) and torch.all(state[:, H * D * V:][[0, 2, 3]] == 0)
 
 
+@pytest.mark.parametrize("H, KH, D, V", [(4, 2, 24, 20), (2, 2, 128, 128), (3, 1, 64, 100)])
+def test_delta_rule_kernel_for_single_tokens(H, KH, D, V):
+    """The decoding form (one token per request and step, norm and gate in the same kernel) against the plain recurrence,
+    several requests side by side, a padding request among them, the state carried from step to step."""
+    from glassbox_b200 import kernels
+    rng = np.random.default_rng(D * V)
+    B, T = 3, 7
+    qkv = rng.standard_normal((B, T, 2 * KH * D + H * V))
+    beta, a, gate = rng.standard_normal((B, T, H)) * 2, rng.standard_normal((B, T, H * D)) * 2, rng.standard_normal((B, T, H * V))
+    dt_bias, a_log, w = rng.standard_normal(H * D), rng.uniform(-2, 0.5, H), rng.standard_normal(V)
+    f = lambda arr: torch.tensor(arr, dtype=torch.float32, device=DEV)
+    state = torch.zeros((5, H * D * V + 3), device=DEV)
+    state[4] = 2.0
+    slots = [3, 0, 2]
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    got = np.zeros((B, T, H * V))
+    for t in range(T):
+        # requests 0, 1, padding, 2
+        meta = _steps_meta([(t, 1), (t, 1), None, (t, 1)], [slots[0], slots[1], 0, slots[2]])
+        rows = [0, 1, None, 2]
+        pick = lambda arr, width: np.stack([arr[b, t] if b is not None else np.zeros(width) for b in rows])
+        att = torch.zeros((4, H * V), device=DEV)
+        kernels.channel_delta_decode(f(pick(qkv, qkv.shape[-1])), f(pick(beta, H)), f(pick(a, H * D)), f(dt_bias), f(a_log), state,
+                                     f(pick(gate, H * V)), f(w), 1e-5, att, meta["first"], meta["start"], meta["slots"], H, KH, D, V,
+                                     True, status)
+        out = att.cpu().numpy()
+        got[0, t], got[1, t], got[2, t] = out[0], out[1], out[3]
+        assert np.all(out[2] == 0)
+    assert int(status.item()) == 0
+    for b in range(B):
+        q = qkv[b][:, :KH * D].reshape(T, KH, D)
+        k = qkv[b][:, KH * D:2 * KH * D].reshape(T, KH, D)
+        q = q / np.sqrt((q * q).sum(-1, keepdims=True) + 1e-6) * D ** -0.5
+        k = k / np.sqrt((k * k).sum(-1, keepdims=True) + 1e-6)
+        q, k = np.repeat(q, H // KH, 1), np.repeat(k, H // KH, 1)
+        g = np.exp(-np.exp(a_log)[None, :, None] * plain.softplus(a[b] + dt_bias).reshape(T, H, D))
+        o = plain.delta_rule(q, k, qkv[b][:, 2 * KH * D:].reshape(T, H, V), g, plain.sigmoid(beta[b]))
+        want = (plain.rms_unit(o, 1e-5) * w * plain.sigmoid(gate[b].reshape(T, H, V))).reshape(T, H * V)
+        np.testing.assert_allclose(got[b], want, atol=5e-5, rtol=2e-4)
+    assert torch.all(state[4] == 2.0) and torch.all(state[1] == 0)
+
+
 def test_branch_norm_head_norm_activation_and_scales():
     from glassbox_b200 import kernels
     rng = np.random.default_rng(9)
