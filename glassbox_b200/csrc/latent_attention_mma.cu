@@ -333,28 +333,51 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(LatentMmaArgs
     }
 }
 
-// One warp per (row, head): merge the shares of the keys and add the sink.
+// One block per (row, head): merge the shares of the keys and add the sink. Thread s weighs share s, thread d sums
+// dimension d over the shares; the loads of a sum do not depend on one another, so they are all in flight together
+// (a warp that walked the shares one after the other paid the trip to memory once per share).
+constexpr int LM_MAX_SPLITS = 64;
+
 __global__ void __launch_bounds__(128) latent_attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                                      const float* __restrict__ sink, const int* __restrict__ positions,
                                                                      __nv_bfloat16* __restrict__ out, int n, int H, int C, int splits) {
+    __shared__ float wgt[LM_MAX_SPLITS];
+    __shared__ float red[4];
     gb_pdl_launch_dependents();
     gb_pdl_wait();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long task = (long long)blockIdx.x * 4 + warp;
-    if (task >= (long long)n * H) return;
-    const int row = (int)(task / H), head = (int)(task % H);
+    const int task = blockIdx.x;
+    const int row = task / H, head = task % H;
     if (positions[row] < 0) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* ml = part_ml + (size_t)task * splits * 2;
-    float m = LM_NEG_BIG;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, ml[2 * s]);
+    const float m_s = tid < splits ? ml[2 * tid] : LM_NEG_BIG;
+    const float l_s = tid < splits ? ml[2 * tid + 1] : 0.f;
+    float m = gb_warp_max(m_s);
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    m = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
     const float sk = sink != nullptr ? sink[head] * LM_LOG2E : LM_NEG_BIG;
     const float mn = fmaxf(m, sk);
-    float l = sink != nullptr ? exp2f(sk - mn) : 0.f;
-    for (int s = 0; s < splits; ++s) l += ml[2 * s + 1] * exp2f(ml[2 * s] - mn);
+    const float w_s = exp2f(m_s - mn);
+    if (tid < splits) wgt[tid] = w_s;
+    float l = gb_warp_sum(l_s * w_s);
+    __syncthreads();                       // (red is read by everyone before it is written again)
+    if (lane == 0) red[warp] = l;
+    __syncthreads();
+    l = red[0] + red[1] + red[2] + red[3] + (sink != nullptr ? exp2f(sk - mn) : 0.f);
     const float inv = l > 0.f ? 1.0f / l : 0.f;
-    for (int d = lane; d < C; d += 32) {
+    for (int d = tid; d < C; d += 128) {
+        const float* po = part_o + (size_t)task * splits * C + d;
         float acc = 0.f;
-        for (int s = 0; s < splits; ++s) acc += part_o[((size_t)task * splits + s) * C + d] * exp2f(ml[2 * s] - mn);
+        int s = 0;
+        for (; s + 8 <= splits; s += 8) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = po[(size_t)(s + j) * C];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc = fmaf(v[j], wgt[s + j], acc);
+        }
+        for (; s < splits; ++s) acc = fmaf(po[(size_t)s * C], wgt[s], acc);
         out[(size_t)task * C + d] = __float2bfloat16_rn(acc * inv);
     }
 }
@@ -398,7 +421,7 @@ GB_EXPORT int gb_latent_attention_mma(const void* q, void* out, float* part_o, f
                                       int* status, cudaStream_t stream) {
     GB_REQUIRE(gb_latent_attention_mma_supported(c, r, page_size), "gb_latent_attention_mma: latent %d, rotated part %d, pages of %d "
                "are outside what the kernel is built for", c, r, page_size);
-    GB_REQUIRE(n >= 0 && S >= 0 && H > 0 && max_pages > 0 && splits >= 1, "gb_latent_attention_mma: bad sizes");
+    GB_REQUIRE(n >= 0 && S >= 0 && H > 0 && max_pages > 0 && splits >= 1 && splits <= LM_MAX_SPLITS, "gb_latent_attention_mma: bad sizes");
     GB_REQUIRE(!decode || splits == 1 || (part_o != nullptr && part_ml != nullptr), "gb_latent_attention_mma: shares of the keys need "
                "buffers for their partial results");
     if (n == 0 || S == 0) return 0;
@@ -417,7 +440,7 @@ GB_EXPORT int gb_latent_attention_mma(const void* q, void* out, float* part_o, f
 #undef LM_CASE
     if (rc) return rc;
     if (decode && splits > 1) {
-        gb_launch(GB_PDL_ATTENTION, latent_attention_merge_kernel, dim3(gb_ceil_div((long long)n * H, 4)), dim3(128), 0, stream,
+        gb_launch(GB_PDL_ATTENTION, latent_attention_merge_kernel, dim3(n * H), dim3(128), 0, stream,
                   (const float*)part_o, (const float*)part_ml, sink, positions, (__nv_bfloat16*)out, n, H, c, splits);
     }
     return gb_check_launch("gb_latent_attention_mma");

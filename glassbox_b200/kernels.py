@@ -925,9 +925,10 @@ def latent_attention_mma_supported(dtype: torch.dtype, c: int, r: int, page_size
     return dtype == torch.bfloat16 and bool(lib().gb_latent_attention_mma_supported(c, r, page_size))
 
 
-def latent_decode_splits(num_seqs: int, heads: int, max_context: int, target_blocks: int = 148 * 2) -> int:
-    """Into how many shares the keys of a decoded row are cut, so that a small batch still fills the GPU: blocks are
-    (share, group of 16 heads, request); a share is at least one tile of 64 keys."""
+def latent_decode_splits(num_seqs: int, heads: int, max_context: int, target_blocks: int = 148 * 5) -> int:
+    """Into how many shares the keys of a decoded row are cut: blocks are (share, group of 16 heads, request), a share is
+    at least one tile of 64 keys, and a block keeps only one tile's load in flight while it works on another, so it
+    takes about five resident blocks per SM (what their shared memory allows) to keep the memory system busy."""
     blocks = max(num_seqs, 1) * -(-heads // 16)
     tiles = max(1, -(-max_context // 64))
     return max(1, min(tiles, -(-target_blocks // blocks), 64))

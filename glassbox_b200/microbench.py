@@ -11,6 +11,9 @@ over operands that rotate through more memory than L2 holds.
     python -m glassbox_b200.microbench small                             embedding, RMSNorm, rotation + cache write, SwiGLU, sampling
     python -m glassbox_b200.microbench decode_program [batch ...]        a decode step as a kernel chain and as a persistent kernel
     python -m glassbox_b200.microbench layer_gemms [rows ...]            the four products of a decode layer as the layer runs them
+    python -m glassbox_b200.microbench latent_attention                  attention over a latent cache (prompt and decoding) beside
+                                                                         grouped-query attention of like size
+    python -m glassbox_b200.microbench delta_rule                        the delta-rule recurrence over a prompt and for single tokens
 
 Prints one line per case: microseconds and GB/s or TFLOP/s of the algorithmic bytes or flops. With ``--once`` after
 the case's name every kernel is launched exactly once and nothing is timed: the form in which a profiler captures one
@@ -159,6 +162,104 @@ def bench_attention_prefill() -> None:
                            reps=6)
             print(f"attention_prefill {name:8s} heads {nh}/{nkv} x {hd}, {t_len} tokens, page {ps}: {t:7.1f} us {fl / t / 1e6:6.1f} TFLOP/s",
                   flush=True)
+    kernels.check_status(status)
+
+
+def bench_latent_attention() -> None:
+    """Latent attention (heads x (64 + rotated), latent 128) beside grouped-query attention with as many heads of size 64:
+    one 2,048-token prompt, and decoding at context 4,096."""
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ps, c = 16, 128
+    for H, r, nkv in [(16, 32, 4), (32, 64, 8)]:
+        w = c + r
+        t_len = 2048
+        per = t_len // ps
+        cache = torch.randn(per + 2, 1, ps, w, device=DEV).bfloat16()
+        tables = torch.arange(per, dtype=torch.int32, device=DEV).view(1, per).contiguous()
+        first = torch.tensor([0, t_len], dtype=torch.int32, device=DEV)
+        start = torch.zeros(1, dtype=torch.int32, device=DEV)
+        pos = torch.arange(t_len, dtype=torch.int32, device=DEV)
+        sink = torch.zeros(H, device=DEV)
+        q = torch.randn(t_len, H * w, device=DEV).bfloat16()
+        o = torch.empty(t_len, H * c, device=DEV).bfloat16()
+        t = graph_time(lambda: kernels.latent_attention_mma(q, o, cache, tables, first, start, pos, sink, H, c, r, ps, w ** -0.5, None,
+                                                            status, max_rows_per_seq=t_len), reps=6)
+        fl = 1.0 * t_len * t_len * H * (w + c)           # scores over c + r and values over c, the causal half
+        print(f"latent_attention prompt  heads {H} latent {c}+{r}, {t_len} tokens: {t:7.1f} us {fl / t / 1e6:6.1f} TFLOP/s", flush=True)
+        hd = 64
+        kc = torch.randn(per + 2, nkv, ps, hd, device=DEV).bfloat16()
+        vc = torch.randn_like(kc)
+        q2 = torch.randn(t_len, H * hd, device=DEV).bfloat16()
+        o2 = torch.empty_like(q2)
+        t = graph_time(lambda: kernels.attention_prefill_tc(q2, o2, kc, vc, tables, first, start, t_len, H, nkv, hd, ps, hd ** -0.5,
+                                                            None, status), reps=6)
+        fl = 2.0 * t_len * t_len * H * hd
+        print(f"   grouped-query prompt  heads {H}/{nkv} x {hd} (tcgen05), {t_len} tokens: {t:7.1f} us {fl / t / 1e6:6.1f} TFLOP/s", flush=True)
+        ctx = 4096
+        for m in (1, 8, 64):
+            per = ctx // ps
+            cache = torch.randn(m * per + 4, 1, ps, w, device=DEV).bfloat16()
+            tables = torch.arange(m * per, dtype=torch.int32, device=DEV).view(m, per).contiguous()
+            first = torch.arange(m + 1, dtype=torch.int32, device=DEV)
+            pos = torch.full((m,), ctx - 1, dtype=torch.int32, device=DEV)
+            q = torch.randn(m, H * w, device=DEV).bfloat16()
+            o = torch.empty(m, H * c, device=DEV).bfloat16()
+            splits = kernels.latent_decode_splits(m, H, ctx)
+            po, pm = torch.empty(m, H * splits * c, device=DEV), torch.empty(m, H * splits * 2, device=DEV)
+            t = graph_time(lambda: kernels.latent_attention_mma(q, o, cache, tables, first, pos, pos, sink, H, c, r, ps, w ** -0.5,
+                                                                None, status, decode=True, splits=splits, part_o=po, part_ml=pm))
+            nbytes = m * ctx * w * 2
+            print(f"latent_attention decode  heads {H} latent {c}+{r} batch {m:3d} ctx {ctx} shares {splits:2d}: {t:7.1f} us "
+                  f"{nbytes / t / 1e3:6.0f} GB/s", flush=True)
+            kc = torch.randn(m * per + 4, nkv, ps, hd, device=DEV).bfloat16()
+            vc = torch.randn_like(kc)
+            row_seq = torch.arange(m, dtype=torch.int32, device=DEV)
+            q2 = torch.randn(m, H * hd, device=DEV).bfloat16()
+            o2 = torch.empty_like(q2)
+            sp, block_keys, warps = kernels.decode_mma_plan(m, nkv, hd, ctx)
+            pa = torch.empty(m * H * warps * sp * hd, device=DEV)
+            pm2 = torch.empty(m * H * warps * sp * 2, device=DEV)
+            cn = torch.zeros(m * nkv, dtype=torch.int32, device=DEV)
+            t = graph_time(lambda: kernels.attention_decode_mma(q2, o2, kc, vc, tables, row_seq, pos, H, nkv, hd, ps, hd ** -0.5, None,
+                                                                sp, pa, pm2, cn, status, block_keys, warps))
+            nbytes = m * ctx * nkv * hd * 2 * 2
+            print(f"   grouped-query decode  heads {H}/{nkv} x {hd} batch {m:3d} ctx {ctx}: {t:7.1f} us {nbytes / t / 1e3:6.0f} GB/s", flush=True)
+    kernels.check_status(status)
+
+
+def bench_delta_rule() -> None:
+    """The recurrence with key and value size 128: a 2,048-token prompt (a chain of 2,048 dependent updates per column of S),
+    and single tokens for 1, 8 and 64 requests (S read and written once: bytes / time)."""
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    dk = dv = 128
+    for H in (8, 16):
+        for n, S in ((2048, 1), (1, 1), (8, 8), (64, 64)):
+            per = n // S
+            qkv = torch.randn(n, 2 * H * dk + H * dv, device=DEV)
+            beta, a, gate = torch.randn(n, H, device=DEV), torch.randn(n, H * dk, device=DEV), torch.randn(n, H * dv, device=DEV)
+            dt, al, w = torch.randn(H * dk, device=DEV), torch.zeros(H, device=DEV), torch.ones(dv, device=DEV)
+            copies = max(1, int(2 * L2_BYTES / (S * H * dk * dv * 4)))            # rotate through more state than L2 holds
+            states = [torch.zeros(S, H * dk * dv, device=DEV) for _ in range(min(copies, 8))]
+            first = torch.arange(0, n + 1, per, dtype=torch.int32, device=DEV)
+            start = torch.zeros(S, dtype=torch.int32, device=DEV)
+            slots = torch.arange(S, dtype=torch.int32, device=DEV)
+            turn = [0]
+            if per == 1:
+                att = torch.empty(n, H * dv, device=DEV).bfloat16()
+
+                def fn():
+                    turn[0] += 1
+                    kernels.channel_delta_decode(qkv, beta, a, dt, al, states[turn[0] % len(states)], gate, w, 1e-6, att, first, start,
+                                                 slots, H, H, dk, dv, True, status)
+                t = graph_time(fn)
+                nbytes = 2.0 * S * H * dk * dv * 4
+                print(f"delta_rule single tokens heads {H} x {dk} x {dv}, {S:2d} requests: {t:7.1f} us {nbytes / t / 1e3:6.0f} GB/s", flush=True)
+            else:
+                out = torch.empty(n, H * dv, device=DEV)
+                t = graph_time(lambda: kernels.channel_delta(qkv, beta, a, dt, al, states[0], out, first, start, slots, H, H, dk, dv,
+                                                             True, status), reps=3)
+                print(f"delta_rule prompt heads {H} x {dk} x {dv}, {n} tokens: {t:7.1f} us = {t / n:5.3f} us per token "
+                      f"({6.0 * n * H * dk * dv / t / 1e6:5.2f} TFLOP/s)", flush=True)
     kernels.check_status(status)
 
 
@@ -344,7 +445,7 @@ def bench_layer_gemms(rows) -> None:
     kernels.check_status(st)
 
 
-CASES = ("gemm_stream", "gemm_tc", "attention_decode", "attention_splits", "attention_prefill", "float32", "small", "decode_program", "layer_gemms")
+CASES = ("gemm_stream", "gemm_tc", "attention_decode", "attention_splits", "attention_prefill", "float32", "small", "decode_program", "layer_gemms", "latent_attention", "delta_rule")
 
 
 def main(argv) -> int:
@@ -374,6 +475,10 @@ def main(argv) -> int:
         bench_decode_program([int(x) for x in argv[1:]])
     elif argv[0] == "layer_gemms":
         bench_layer_gemms([int(x) for x in argv[1:]])
+    elif argv[0] == "latent_attention":
+        bench_latent_attention()
+    elif argv[0] == "delta_rule":
+        bench_delta_rule()
     else:
         bench_attention_prefill()
     return 0

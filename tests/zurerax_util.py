@@ -47,6 +47,12 @@ CONFIGS = {
         latent(16, 16, 16, 16, 64, base=20000.0, kv_from=1, mlp=128),
         delta(2, 2, 128, 32, 4, 16, 4, mlp=128),
     ], embedding_scale=11.3, logit_scale=2.5),
+    # sizes that fit no vector width: odd row lengths everywhere, so every kernel's aligned fast path must step aside
+    "ragged": lambda: config(67, 50, [
+        latent(3, 10, 6, 7, 9, base=300.0, mlp=30),
+        delta(3, 1, 10, 7, 3, 3, 5, mlp=None),
+        latent(5, 6, 6, 3, 9, base=300.0, kv_from=0, mlp=22),
+    ], embedding_scale=2.0, logit_scale=1.3),
     # ones: one head, one tap (no convolution state), rank one, no feed-forward anywhere
     "ones": lambda: config(97, 40, [
         delta(1, 1, 8, 8, 1, 1, 1),
