@@ -1,5 +1,5 @@
 """glassbox_b200: a small, whole inference engine for one B200, for the Llama-family decoder
-that Glassbox runs (SmolLM2): typed configuration and an architecture registry (``config``, ``models``),
+that Glassbox runs (SmolLM2) and for Zurerax (delta-rule and latent-attention layers): typed configuration and an architecture registry (``config``, ``models``),
 safetensors weights (``weights``), layers put together from parts (``parts``), a paged cache manager
 (``cache``), one step function, a scheduler and trace replay (``engine``), sampling, and hand-written CUDA
 kernels for sm_100a (``csrc``, called through ``kernels``)."""
