@@ -92,7 +92,8 @@ GB_EXPORT int gb_short_conv(const float* x, long long ldx, const float* w, float
 // Walkers: a thread owns DPT rows of one column of S in registers: lane = column * NS + split, so the NS splits of a
 // column are neighbouring lanes and the two reductions over the key dimension are shuffles. Per token the chain that
 // cannot be shortened is: decay, dot with k, reduce, u, update; the read-out's own reduction is put off by one token
-// and rides in the same shuffle rounds as the next token's dot product.
+// and rides in the same shuffle rounds as the next token's dot product, and the next token's decays and keys are read
+// from shared memory while those rounds are under way.
 // Stagers: meanwhile the other eight warps prepare the next TC tokens in the second shared-memory buffer: every load
 // of a batch is asked for before the first is used (instructions issue in order: a loop that uses each value as it
 // arrives pays the trip to memory once per round), decays are evaluated (exp(-r * softplus(z)) = exp(-r * log(1 + e^z))
@@ -122,7 +123,7 @@ struct ChannelDeltaArgs {
     int* status;
 };
 
-template <int DPT>
+template <int DPT, int NS>
 __global__ void __launch_bounds__(CD_THREADS) channel_delta_kernel(ChannelDeltaArgs p) {
     extern __shared__ __align__(16) float cd_smem[];
     gb_pdl_launch_dependents();
@@ -135,13 +136,13 @@ __global__ void __launch_bounds__(CD_THREADS) channel_delta_kernel(ChannelDeltaA
         return;
     }
     const int r0 = p.seq_first_row[seq], r1 = p.seq_first_row[seq + 1];
-    const int NS = p.ns, TC = p.tc, dk = p.dk, dv = p.dv;
-    const int cols = CD_GROUP / NS;                        // columns of S per block
+    const int TC = p.tc, dk = p.dk, dv = p.dv;
+    constexpr int cols = CD_GROUP / NS;                    // columns of S per block
     const bool walker = threadIdx.x < CD_GROUP;
     const int wt = walker ? threadIdx.x : threadIdx.x - CD_GROUP;     // index within the group
     const int kvh = head / (p.heads / p.kv_heads);
     constexpr int PAD = DPT + 4;                           // a split's numbers start 16-byte aligned, on other banks than its neighbours'
-    const int row_w = NS * PAD, Dp = NS * DPT;             // Dp: the key size rounded up (a power of two)
+    constexpr int row_w = NS * PAD, Dp = NS * DPT;         // Dp: the key size rounded up (a power of two)
     const int dp_shift = 31 - __clz(Dp), cols_shift = 31 - __clz(cols);
     const int per_token = 3 * row_w + cols + 4;
     const int buf_floats = TC * per_token;
@@ -244,17 +245,34 @@ __global__ void __launch_bounds__(CD_THREADS) channel_delta_kernel(ChannelDeltaA
             const float* sc = vs + (size_t)TC * cols;
             const int c0 = r0 + chunk * TC;
             const int nt = min(TC, r1 - c0);
+            // the decays and keys of the token after this one are asked for while this token's sums travel the lanes
+            constexpr bool AHEAD = DPT <= 16;              // (with 32 rows per thread the registers do not reach)
+            float4 gn[DPT / 4], kn[DPT / 4];
+            if (AHEAD) {
+#pragma unroll
+                for (int i = 0; i < DPT / 4; ++i) {
+                    gn[i] = reinterpret_cast<const float4*>(gs + split * PAD)[i];
+                    kn[i] = reinterpret_cast<const float4*>(ks + split * PAD)[i];
+                }
+            }
             for (int t = 0; t < nt; ++t) {
-                const float4* g4 = reinterpret_cast<const float4*>(gs + t * row_w + split * PAD);
-                const float4* k4 = reinterpret_cast<const float4*>(ks + t * row_w + split * PAD);
+                if (!AHEAD) {
+#pragma unroll
+                    for (int i = 0; i < DPT / 4; ++i) {
+                        gn[i] = reinterpret_cast<const float4*>(gs + t * row_w + split * PAD)[i];
+                        kn[i] = reinterpret_cast<const float4*>(ks + t * row_w + split * PAD)[i];
+                    }
+                }
                 const float4* q4 = reinterpret_cast<const float4*>(qs + t * row_w + split * PAD);
                 const float4 scal = *reinterpret_cast<const float4*>(sc + t * 4);      // beta, 1/|q| / sqrt(dk), 1/|k|
                 const float vt = vs[t * cols + col_local];
+                float4 qv[DPT / 4];
                 float kk[DPT];
                 float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
                 for (int i = 0; i < DPT / 4; ++i) {
-                    const float4 g = g4[i], k = k4[i];
+                    const float4 g = gn[i], k = kn[i];
+                    qv[i] = q4[i];
                     kk[4 * i] = k.x; kk[4 * i + 1] = k.y; kk[4 * i + 2] = k.z; kk[4 * i + 3] = k.w;
                     S[4 * i] *= g.x; S[4 * i + 1] *= g.y; S[4 * i + 2] *= g.z; S[4 * i + 3] *= g.w;
                     a0 = fmaf(S[4 * i], k.x, a0);
@@ -262,7 +280,15 @@ __global__ void __launch_bounds__(CD_THREADS) channel_delta_kernel(ChannelDeltaA
                     a2 = fmaf(S[4 * i + 2], k.z, a2);
                     a3 = fmaf(S[4 * i + 3], k.w, a3);
                 }
+                if (AHEAD && t + 1 < nt) {
+#pragma unroll
+                    for (int i = 0; i < DPT / 4; ++i) {
+                        gn[i] = reinterpret_cast<const float4*>(gs + (t + 1) * row_w + split * PAD)[i];
+                        kn[i] = reinterpret_cast<const float4*>(ks + (t + 1) * row_w + split * PAD)[i];
+                    }
+                }
                 float sk = (a0 + a1) + (a2 + a3);
+#pragma unroll
                 for (int o = 1; o < NS; o <<= 1) {       // this token's dot product and the last token's read-out, together
                     sk += __shfl_xor_sync(0xffffffffu, sk, o);
                     o_part += __shfl_xor_sync(0xffffffffu, o_part, o);
@@ -272,7 +298,7 @@ __global__ void __launch_bounds__(CD_THREADS) channel_delta_kernel(ChannelDeltaA
                 a0 = a1 = a2 = a3 = 0.f;
 #pragma unroll
                 for (int i = 0; i < DPT / 4; ++i) {
-                    const float4 q = q4[i];
+                    const float4 q = qv[i];
                     S[4 * i] = fmaf(kk[4 * i], u, S[4 * i]);
                     S[4 * i + 1] = fmaf(kk[4 * i + 1], u, S[4 * i + 1]);
                     S[4 * i + 2] = fmaf(kk[4 * i + 2], u, S[4 * i + 2]);
@@ -289,6 +315,7 @@ __global__ void __launch_bounds__(CD_THREADS) channel_delta_kernel(ChannelDeltaA
         __syncthreads();
     }
     if (walker) {
+#pragma unroll
         for (int o = 1; o < NS; o <<= 1) o_part += __shfl_xor_sync(0xffffffffu, o_part, o);
         if (o_row >= 0 && split == 0 && live) p.out[(size_t)o_row * p.heads * dv + (size_t)head * dv + col] = o_part;
         if (p.write_state) {
@@ -321,16 +348,20 @@ GB_EXPORT int gb_channel_delta(const float* qkv, long long ldq, const float* bet
                           seq_slots, heads, kv_heads, dk, dv, ns, tc, num_slots, write_state, status};
     dim3 grid(S, heads, gb_ceil_div(dv, cols));
     const size_t smem = (size_t)2 * tc * per_token;
-    static bool raised = false;
-    if (!raised) {
-        cudaFuncSetAttribute(channel_delta_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-        cudaFuncSetAttribute(channel_delta_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-        raised = true;
+    bool launched = false;
+#define CD_CASE(D, N)                                                                                              \
+    if (!launched && dpt == D && ns == N) {                                                                        \
+        static bool raised = false;                                                                                \
+        if (!raised) {                                                                                             \
+            cudaFuncSetAttribute(channel_delta_kernel<D, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); \
+            raised = true;                                                                                         \
+        }                                                                                                          \
+        gb_launch(GB_PDL_ATTENTION, channel_delta_kernel<D, N>, grid, dim3(CD_THREADS), smem, stream, p);          \
+        launched = true;                                                                                           \
     }
-    if (dpt == 16)
-        gb_launch(GB_PDL_ATTENTION, channel_delta_kernel<16>, grid, dim3(CD_THREADS), smem, stream, p);
-    else
-        gb_launch(GB_PDL_ATTENTION, channel_delta_kernel<32>, grid, dim3(CD_THREADS), smem, stream, p);
+    CD_CASE(16, 1) CD_CASE(16, 2) CD_CASE(16, 4) CD_CASE(16, 8) CD_CASE(32, 8) CD_CASE(32, 16) CD_CASE(32, 32)
+#undef CD_CASE
+    GB_REQUIRE(launched, "gb_channel_delta: no kernel for a key size of %d", dk);
     return gb_check_launch("gb_channel_delta");
 }
 
