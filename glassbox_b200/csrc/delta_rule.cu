@@ -374,10 +374,60 @@ GB_EXPORT int gb_channel_delta(const float* qkv, long long ldq, const float* bet
 // too (the block holds the whole head): the output is the mixer's activation, ready for its output projection.
 // Key and value sizes up to 128.
 // ----------------------------------------------------------------------------------------------
-template <typename T>
+// What the fused form reads instead of finished q, k, v, decay logits and gate logits: the stacked projection's raw row
+// (q | k | v channels before their convolutions, then the low-rank inputs of the decay and of the gate), the
+// convolutions' weights and last inputs, and the two second-level matrices.
+struct DeltaDecodeFusion {
+    const float* proj;       // [n, ldp]
+    long long ldp;
+    const float* conv_w;     // [channels, taps]
+    long long conv_state_off;
+    int taps, channels, a1_at, ra, rg;      // the gate's low-rank input follows the decay's
+    const void* w_a2;        // [heads * dk, ra]
+    const void* w_g2;        // [heads * dv, rg]
+};
+constexpr int CD_MAX_LOW_RANK = 512;        // ra + rg
+
+template <typename TW>
+__device__ __forceinline__ float cd_dot_row(const TW* __restrict__ w, const float* __restrict__ x, int n) {
+    float acc = 0.f;
+    for (int i = 0; i < n; ++i) acc = fmaf(gb_to_float(w[i]), x[i], acc);
+    return acc;
+}
+template <>
+__device__ __forceinline__ float cd_dot_row<__nv_bfloat16>(const __nv_bfloat16* __restrict__ w, const float* __restrict__ x, int n) {
+    float a0 = 0.f, a1 = 0.f;
+    int i = 0;
+    if ((((uintptr_t)w) & 15) == 0) {
+        for (; i + 8 <= n; i += 8) {        // eight weights per load
+            const uint4 v = *reinterpret_cast<const uint4*>(w + i);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                a0 = fmaf(__low2float(h[j]), x[i + 2 * j], a0);
+                a1 = fmaf(__high2float(h[j]), x[i + 2 * j + 1], a1);
+            }
+        }
+    }
+    for (; i < n; ++i) a0 = fmaf(__bfloat162float(w[i]), x[i], a0);
+    return a0 + a1;
+}
+
+// One causal convolution output for a single new token: the slot's taps - 1 last inputs, then the token's own.
+__device__ __forceinline__ float cd_conv_one(const DeltaDecodeFusion& f, const float* __restrict__ st, size_t row, int ch) {
+    float acc = f.conv_w[(size_t)ch * f.taps + f.taps - 1] * f.proj[row * f.ldp + ch];
+    for (int j = 0; j < f.taps - 1; ++j) acc = fmaf(f.conv_w[(size_t)ch * f.taps + j], st[(size_t)j * f.channels + ch], acc);
+    return acc / (1.0f + expf(-acc));
+}
+
+// FUSED: the convolutions of q, k, v (reading the slot's last inputs; the shift is left to the kernel that follows)
+// and the two low-rank second-level products are computed here, from the stacked projection's row.
+template <typename T, typename TW, bool FUSED>
 __global__ void __launch_bounds__(256) channel_delta_decode_kernel(ChannelDeltaArgs p, const float* __restrict__ gate, long long ldg,
-                                                                   const float* __restrict__ norm_w, float eps, T* __restrict__ att) {
-    __shared__ float qs[128], ks[128], gs[128], part[8][128], ovec[128], red[16];
+                                                                   const float* __restrict__ norm_w, float eps, T* __restrict__ att,
+                                                                   DeltaDecodeFusion f) {
+    __shared__ float qs[128], ks[128], gs[128], part[8][128], ovec[128], red[16], vsm[128], gsm[128];
+    __shared__ float lr[FUSED ? CD_MAX_LOW_RANK : 1];
     gb_pdl_launch_dependents();
     gb_pdl_wait();
     const int seq = blockIdx.x, head = blockIdx.y;
@@ -404,16 +454,32 @@ __global__ void __launch_bounds__(256) channel_delta_decode_kernel(ChannelDeltaA
     }
     // the token's vectors: thread d takes key channel d
     float qv = 0.f, kv = 0.f, zv = -1e30f;
-    if (tid < dk) {
-        qv = p.qkv[row * p.ldq + (size_t)kvh * dk + tid];
-        kv = p.qkv[row * p.ldq + (size_t)(p.kv_heads + kvh) * dk + tid];
-        zv = p.a[row * p.lda + (size_t)head * dk + tid] + p.dt_bias[(size_t)head * dk + tid];
-    }
     float vt[4];
+    if (FUSED) {
+        for (int i = tid; i < f.ra + f.rg; i += 256) lr[i] = f.proj[row * f.ldp + f.a1_at + i];
+        __syncthreads();
+        const float* st = p.state + (size_t)slot * p.state_stride + f.conv_state_off;
+        if (tid < dk) {
+            qv = cd_conv_one(f, st, row, kvh * dk + tid);
+            kv = cd_conv_one(f, st, row, (p.kv_heads + kvh) * dk + tid);
+            zv = cd_dot_row(reinterpret_cast<const TW*>(f.w_a2) + ((size_t)head * dk + tid) * f.ra, lr, f.ra) +
+                 p.dt_bias[(size_t)head * dk + tid];
+        } else if (tid >= 128 && tid - 128 < dv) {      // the other half of the block: values and gate logits
+            const int j = tid - 128;
+            vsm[j] = cd_conv_one(f, st, row, 2 * p.kv_heads * dk + head * dv + j);
+            gsm[j] = cd_dot_row(reinterpret_cast<const TW*>(f.w_g2) + ((size_t)head * dv + j) * f.rg, lr + f.ra, f.rg);
+        }
+    } else {
+        if (tid < dk) {
+            qv = p.qkv[row * p.ldq + (size_t)kvh * dk + tid];
+            kv = p.qkv[row * p.ldq + (size_t)(p.kv_heads + kvh) * dk + tid];
+            zv = p.a[row * p.lda + (size_t)head * dk + tid] + p.dt_bias[(size_t)head * dk + tid];
+        }
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-        const int col = lane + 32 * c;
-        vt[c] = col < dv ? p.qkv[row * p.ldq + (size_t)2 * p.kv_heads * dk + (size_t)head * dv + col] : 0.f;
+        for (int c = 0; c < 4; ++c) {
+            const int col = lane + 32 * c;
+            vt[c] = col < dv ? p.qkv[row * p.ldq + (size_t)2 * p.kv_heads * dk + (size_t)head * dv + col] : 0.f;
+        }
     }
     const float beta = 1.0f / (1.0f + __expf(-p.beta[row * p.ldb + head]));
     if (tid < 128) {
@@ -425,6 +491,10 @@ __global__ void __launch_bounds__(256) channel_delta_decode_kernel(ChannelDeltaA
         if (lane == 0) { red[warp] = sq; red[4 + warp] = sk; }
     }
     __syncthreads();
+    if (FUSED) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) vt[c] = lane + 32 * c < dv ? vsm[lane + 32 * c] : 0.f;
+    }
     const float iq = 1.0f / sqrtf((float)dk) / sqrtf(red[0] + red[1] + red[2] + red[3] + CD_UNIT_EPS);
     const float ik = 1.0f / sqrtf(red[4] + red[5] + red[6] + red[7] + CD_UNIT_EPS);
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -486,7 +556,7 @@ __global__ void __launch_bounds__(256) channel_delta_decode_kernel(ChannelDeltaA
     __syncthreads();
     if (tid < dv) {
         const float s = 1.0f / sqrtf((red[8] + red[9] + red[10] + red[11]) / (float)dv + eps);
-        const float sig = 1.0f / (1.0f + expf(-gate[row * ldg + (size_t)head * dv + tid]));
+        const float sig = 1.0f / (1.0f + expf(-(FUSED ? gsm[tid] : gate[row * ldg + (size_t)head * dv + tid])));
         att[row * p.heads * dv + (size_t)head * dv + tid] = gb_from_float<T>(ovec[tid] * s * norm_w[tid] * sig);
     }
 }
@@ -494,24 +564,55 @@ __global__ void __launch_bounds__(256) channel_delta_decode_kernel(ChannelDeltaA
 GB_EXPORT int gb_channel_delta_decode_supported(int dk, int dv) { return dk > 0 && dk <= 128 && dv > 0 && dv <= 128; }
 
 // Every sequence of the step brings exactly one row. att: [n, heads * dv] in `att_dtype`, the gated and normed read-out.
+// With proj != nullptr the fused form runs: qkv, a and gate are not read; the convolutions (without the shift of the
+// slot's last inputs: gb_short_conv_state does that afterwards) and the low-rank products are computed in the kernel
+// from the stacked projection `proj` (columns: conv channels, then at `a1_at` the decay's and the gate's low-rank inputs).
 GB_EXPORT int gb_channel_delta_decode(const float* qkv, long long ldq, const float* beta, long long ldb, const float* a, long long lda,
                                       const float* dt_bias, const float* a_log, float* state, long long state_stride,
                                       const float* gate, long long ldg, const float* norm_w, float eps, void* att, int att_dtype,
                                       const int* seq_first_row, const int* seq_start_pos, const int* seq_slots, int S, int heads,
-                                      int kv_heads, int dk, int dv, int num_slots, int write_state, int* status, cudaStream_t stream) {
+                                      int kv_heads, int dk, int dv, int num_slots, int write_state, int* status,
+                                      const float* proj, long long ldp, const float* conv_w, long long conv_state_off, int taps,
+                                      int a1_at, int ra, int rg, const void* w_a2, const void* w_g2, int w_dtype,
+                                      cudaStream_t stream) {
     GB_REQUIRE(S >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "gb_channel_delta_decode: heads %d must be a multiple of "
                "key heads %d", heads, kv_heads);
     GB_REQUIRE(gb_channel_delta_decode_supported(dk, dv), "gb_channel_delta_decode: key size %d and value size %d must be at most 128", dk, dv);
+    const bool fused = proj != nullptr;
+    GB_REQUIRE(!fused || (ra > 0 && rg > 0 && ra + rg <= CD_MAX_LOW_RANK && taps >= 1 && conv_w && w_a2 && w_g2),
+               "gb_channel_delta_decode: the fused form takes low ranks up to %d in all", CD_MAX_LOW_RANK);
     if (S == 0) return 0;
     ChannelDeltaArgs p = {qkv, ldq, beta, ldb, a, lda, dt_bias, a_log, state, state_stride, nullptr, seq_first_row, seq_start_pos,
                           seq_slots, heads, kv_heads, dk, dv, 0, 0, num_slots, write_state, status};
+    DeltaDecodeFusion f = {proj, ldp, conv_w, conv_state_off, taps, 2 * kv_heads * dk + heads * dv, a1_at, ra, rg, w_a2, w_g2};
     dim3 grid(S, heads);
-    if (att_dtype == GB_F32)
-        gb_launch(GB_PDL_ATTENTION, channel_delta_decode_kernel<float>, grid, dim3(256), 0, stream, p, gate, ldg, norm_w, eps, (float*)att);
-    else if (att_dtype == GB_BF16)
-        gb_launch(GB_PDL_ATTENTION, channel_delta_decode_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, p, gate, ldg, norm_w, eps,
-                  (__nv_bfloat16*)att);
-    else
-        GB_REQUIRE(false, "gb_channel_delta_decode: unsupported output dtype %d", att_dtype);
+#define CDD_LAUNCH(T, TW, F) gb_launch(GB_PDL_ATTENTION, channel_delta_decode_kernel<T, TW, F>, grid, dim3(256), 0, stream, p, gate, ldg, \
+                                        norm_w, eps, (T*)att, f)
+    if (att_dtype != GB_F32 && att_dtype != GB_BF16) GB_REQUIRE(false, "gb_channel_delta_decode: unsupported output dtype %d", att_dtype);
+    if (!fused) {
+        if (att_dtype == GB_F32) CDD_LAUNCH(float, float, false);
+        else CDD_LAUNCH(__nv_bfloat16, float, false);
+    } else if (w_dtype == GB_F32) {
+        if (att_dtype == GB_F32) CDD_LAUNCH(float, float, true);
+        else CDD_LAUNCH(__nv_bfloat16, float, true);
+    } else if (w_dtype == GB_BF16) {
+        if (att_dtype == GB_F32) CDD_LAUNCH(float, __nv_bfloat16, true);
+        else CDD_LAUNCH(__nv_bfloat16, __nv_bfloat16, true);
+    } else {
+        GB_REQUIRE(false, "gb_channel_delta_decode: unsupported weight dtype %d", w_dtype);
+    }
+#undef CDD_LAUNCH
     return gb_check_launch("gb_channel_delta_decode");
+}
+
+// The shift-and-append of the convolutions' last inputs alone (after a kernel that computed the convolutions itself).
+GB_EXPORT int gb_short_conv_state(const float* x, long long ldx, float* state, long long state_stride, long long state_off,
+                                  const int* seq_first_row, const int* seq_start_pos, const int* seq_slots, int S, int C, int taps,
+                                  int num_slots, cudaStream_t stream) {
+    GB_REQUIRE(S >= 0 && C > 0 && taps >= 1 && taps <= 64, "gb_short_conv_state: bad sizes (taps %d)", taps);
+    if (S == 0 || taps == 1) return 0;
+    dim3 grid(S, gb_ceil_div(C, 256));
+    gb_launch(GB_PDL_ELEMENTWISE, short_conv_state_kernel, grid, dim3(256), 0, stream, x, ldx, state, state_stride, state_off,
+              seq_first_row, seq_start_pos, seq_slots, S, C, taps, num_slots);
+    return gb_check_launch("gb_short_conv_state");
 }

@@ -90,7 +90,8 @@ _SIGNATURES = {
     "gb_channel_delta": [_P, _LL, _P, _LL, _P, _LL, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "gb_channel_delta_decode_supported": [_I, _I],
     "gb_channel_delta_decode": [_P, _LL, _P, _LL, _P, _LL, _P, _P, _P, _LL, _P, _LL, _P, _F, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I,
-                                _I, _I, _P, _P],
+                                _I, _I, _P, _P, _LL, _P, _LL, _I, _I, _I, _I, _P, _P, _I, _P],
+    "gb_short_conv_state": [_P, _LL, _P, _LL, _LL, _P, _P, _P, _I, _I, _I, _I, _P],
     "gb_program_op_bytes": [],
     "gb_program_max_rows": [],
 }
@@ -1003,22 +1004,71 @@ def channel_delta_decode_supported(dk: int, dv: int) -> bool:
     return bool(lib().gb_channel_delta_decode_supported(dk, dv))
 
 
-def channel_delta_decode(qkv: torch.Tensor, beta: torch.Tensor, a: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor,
-                         state: torch.Tensor, gate: torch.Tensor, norm_weight: torch.Tensor, eps: float, att: torch.Tensor,
-                         seq_first_row: torch.Tensor, seq_start_pos: torch.Tensor, seq_slots: torch.Tensor, heads: int,
-                         kv_heads: int, dk: int, dv: int, write_state: bool, status: torch.Tensor) -> None:
+class DeltaDecodeFusion:
+    """What the fused decoding form of the delta rule reads instead of finished q, k, v, decay and gate logits: the stacked
+    projection's raw rows ``proj`` float32 [n, >= conv channels + ranks] (q | k | v channels before their convolutions; at
+    column ``a1_at`` the low-rank input of the decay, ``w_a2.shape[1]`` numbers, then that of the gate), the convolutions'
+    weights [channels, taps] and where in a slot their last inputs start, and the two second-level matrices."""
+    __slots__ = ("proj", "conv_w", "conv_state_off", "a1_at", "w_a2", "w_g2")
+
+    def __init__(self, proj, conv_w, conv_state_off, a1_at, w_a2, w_g2):
+        self.proj, self.conv_w, self.conv_state_off, self.a1_at, self.w_a2, self.w_g2 = proj, conv_w, conv_state_off, a1_at, w_a2, w_g2
+
+    @staticmethod
+    def supported(w_a2: torch.Tensor, w_g2: torch.Tensor) -> bool:
+        return (w_a2.dtype == w_g2.dtype and w_a2.dtype in _DT and w_a2.is_contiguous() and w_g2.is_contiguous()
+                and w_a2.shape[1] + w_g2.shape[1] <= 512)
+
+
+def channel_delta_decode(qkv: Optional[torch.Tensor], beta: torch.Tensor, a: Optional[torch.Tensor], dt_bias: torch.Tensor,
+                         a_log: torch.Tensor, state: torch.Tensor, gate: Optional[torch.Tensor], norm_weight: torch.Tensor,
+                         eps: float, att: torch.Tensor, seq_first_row: torch.Tensor, seq_start_pos: torch.Tensor,
+                         seq_slots: torch.Tensor, heads: int, kv_heads: int, dk: int, dv: int, write_state: bool,
+                         status: torch.Tensor, fusion: Optional[DeltaDecodeFusion] = None) -> None:
     """``channel_delta`` for a step in which every request brings one row, with the read-out's norm and gate applied as
     well: ``att`` [n, heads * dv] (any activation dtype) = norm_weight * o / rms(o) * sigmoid(gate). Reads and writes
-    each request's S once, in whole rows."""
+    each request's S once, in whole rows. With ``fusion`` the kernel also computes the convolutions of q, k, v (reading
+    the slot's last inputs; ``short_conv_state`` must shift them afterwards) and the two low-rank products itself:
+    ``qkv``, ``a`` and ``gate`` are then None."""
     _cuda(qkv, beta, a, dt_bias, a_log, state, gate, norm_weight, att, seq_first_row, seq_start_pos, seq_slots, status)
-    n = qkv.shape[0]
-    for t in (qkv, beta, a, dt_bias, a_log, state, gate, norm_weight):
+    n = beta.shape[0]
+    for t in (beta, dt_bias, a_log, state, norm_weight):
         assert t.dtype == torch.float32
-    assert qkv.shape[1] == 2 * kv_heads * dk + heads * dv and qkv.stride(1) == 1 and beta.shape == (n, heads)
-    assert a.shape == (n, heads * dk) and a.stride(1) == 1 and beta.stride(1) == 1 and gate.shape == (n, heads * dv)
-    assert gate.stride(1) == 1 and att.shape == (n, heads * dv) and att.is_contiguous()
+    assert beta.shape == (n, heads) and beta.stride(1) == 1 and att.shape == (n, heads * dv) and att.is_contiguous()
     assert state.dim() == 2 and state.is_contiguous() and state.shape[1] >= heads * dk * dv and norm_weight.numel() == dv
-    _call("gb_channel_delta_decode", _ptr(qkv), qkv.stride(0), _ptr(beta), beta.stride(0), _ptr(a), a.stride(0), _ptr(dt_bias),
-          _ptr(a_log), _ptr(state), state.stride(0), _ptr(gate), gate.stride(0), _ptr(norm_weight), float(eps), _ptr(att),
+    if fusion is None:
+        for t in (qkv, a, gate):
+            assert t.dtype == torch.float32 and t.stride(1) == 1
+        assert qkv.shape == (n, 2 * kv_heads * dk + heads * dv) and a.shape == (n, heads * dk) and gate.shape == (n, heads * dv)
+        extra = (0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0)
+        ptrs = (_ptr(qkv), qkv.stride(0), _ptr(a), a.stride(0), _ptr(gate), gate.stride(0))
+    else:
+        f = fusion
+        _cuda(f.proj, f.conv_w, f.w_a2, f.w_g2)
+        channels = 2 * kv_heads * dk + heads * dv
+        ra, rg = f.w_a2.shape[1], f.w_g2.shape[1]
+        taps = f.conv_w.shape[1]
+        assert DeltaDecodeFusion.supported(f.w_a2, f.w_g2) and f.proj.dtype == f.conv_w.dtype == torch.float32
+        assert f.proj.shape[0] == n and f.proj.stride(1) == 1 and f.proj.shape[1] >= f.a1_at + ra + rg and f.a1_at >= channels
+        assert f.conv_w.shape == (channels, taps) and f.conv_w.is_contiguous()
+        assert f.w_a2.shape[0] == heads * dk and f.w_g2.shape[0] == heads * dv
+        assert f.conv_state_off + (taps - 1) * channels <= state.shape[1]
+        extra = (_ptr(f.proj), f.proj.stride(0), _ptr(f.conv_w), f.conv_state_off, taps, f.a1_at, ra, rg, _ptr(f.w_a2), _ptr(f.w_g2),
+                 _dt(f.w_a2))
+        ptrs = (0, 0, 0, 0, 0, 0)
+    _call("gb_channel_delta_decode", ptrs[0], ptrs[1], _ptr(beta), beta.stride(0), ptrs[2], ptrs[3], _ptr(dt_bias),
+          _ptr(a_log), _ptr(state), state.stride(0), ptrs[4], ptrs[5], _ptr(norm_weight), float(eps), _ptr(att),
           _dt(att), _ptr(seq_first_row), _ptr(seq_start_pos), _ptr(seq_slots), seq_start_pos.shape[0], heads, kv_heads, dk, dv,
-          state.shape[0], 1 if write_state else 0, _ptr(status), _stream())
+          state.shape[0], 1 if write_state else 0, _ptr(status), *extra, _stream())
+
+
+def short_conv_state(x: torch.Tensor, state: torch.Tensor, state_off: int, taps: int, seq_first_row: torch.Tensor,
+                     seq_start_pos: torch.Tensor, seq_slots: torch.Tensor) -> None:
+    """The second half of ``short_conv`` alone: each request's slot keeps the last taps - 1 rows of ``x`` [n, channels]
+    (shifting in what it held when the request brings fewer rows)."""
+    _cuda(x, state, seq_first_row, seq_start_pos, seq_slots)
+    n, C = x.shape
+    assert x.dtype == state.dtype == torch.float32 and x.stride(1) == 1 and state.dim() == 2 and state.is_contiguous()
+    assert state_off + (taps - 1) * C <= state.shape[1]
+    _call("gb_short_conv_state", _ptr(x), x.stride(0), _ptr(state), state.stride(0), state_off, _ptr(seq_first_row),
+          _ptr(seq_start_pos), _ptr(seq_slots), seq_start_pos.shape[0], C, taps, state.shape[0], _stream())
