@@ -8,7 +8,10 @@
 //   gb_short_conv        y[t, c] = silu(sum_j w[c, j] x[t - (taps-1) + j, c]), inputs before a portion's first row come
 //                        from the request's state slot (zeros for a fresh request)
 //   gb_short_conv_state  afterwards: the last taps-1 inputs of each request go to its slot
-//   gb_channel_delta     the recurrence; columns of S are independent, so a head is shared between blocks by columns
+//   gb_channel_delta     the recurrence over runs of tokens; columns of S are independent, so a head is shared between
+//                        blocks by columns
+//   gb_channel_delta_decode  the recurrence for steps of single tokens, with the read-out's norm and gate, and (fused
+//                        form) the convolutions and the low-rank products of the decay and the gate
 #include "common.cuh"
 
 // ----------------------------------------------------------------------------------------------

@@ -11,7 +11,7 @@
 //                    buffers), every warp taking the whole tile for its own 16 rows
 //   decoding         one block = one tile (one token of one request, a head group) and one share of the keys; the four
 //                    warps take a quarter of each 64-key tile for the same 16 rows and merge at the end; several shares
-//                    leave (m, l, O) in float32 and gb_latent_attention_merge finishes
+//                    leave (m, l, O) in float32 and latent_attention_merge_kernel finishes
 //
 // The sink logit of a head joins the denominator once, at the very end (in the merge when the keys are shared).
 #include "common.cuh"
