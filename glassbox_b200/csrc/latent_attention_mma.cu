@@ -136,24 +136,27 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(LatentMmaArgs
         }
     }
 
+    // Two threads per key of the tile: one page look-up and one address per thread, then half a row of 16-byte pieces.
+    static_assert(CPR % 2 == 0, "a cached row is an even number of 16-byte pieces");
     auto load_tile = [&](int kt, int buf) {
-        __nv_bfloat16* dst = Ks + (size_t)buf * LM_BN * WS;
-        for (int c = threadIdx.x; c < LM_BN * CPR; c += 128) {
-            const int kk = c / CPR, ch = c % CPR;
-            const int key = kt * LM_BN + kk;
-            long long page = -1;
-            if (key <= pos_hi) {
-                page = table[key >> p.page_shift];
-                if (page < 0 || page >= p.num_pages) {
-                    if (key >= key_lo) atomicOr(p.status, GB_STATUS_BAD_SLOT);   // (pages behind a window may be gone)
-                    page = -1;
-                }
+        const int kk = threadIdx.x >> 1, half = threadIdx.x & 1;
+        const int key = kt * LM_BN + kk;
+        long long page = -1;
+        if (key <= pos_hi) {
+            page = table[key >> p.page_shift];
+            if (page < 0 || page >= p.num_pages) {
+                if (key >= key_lo) atomicOr(p.status, GB_STATUS_BAD_SLOT);   // (pages behind a window may be gone)
+                page = -1;
             }
-            __nv_bfloat16* d = dst + kk * WS + ch * 8;
-            if (page >= 0)
-                __pipeline_memcpy_async(d, p.cache + ((size_t)page * page_size + (key & (page_size - 1))) * W + ch * 8, 16);
-            else
-                *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        __nv_bfloat16* d = Ks + (size_t)buf * LM_BN * WS + kk * WS + half * (CPR / 2) * 8;
+        if (page >= 0) {
+            const __nv_bfloat16* src = p.cache + ((size_t)page * page_size + (key & (page_size - 1))) * W + half * (CPR / 2) * 8;
+#pragma unroll
+            for (int j = 0; j < CPR / 2; ++j) __pipeline_memcpy_async(d + j * 8, src + j * 8, 16);
+        } else {
+#pragma unroll
+            for (int j = 0; j < CPR / 2; ++j) *reinterpret_cast<uint4*>(d + j * 8) = make_uint4(0u, 0u, 0u, 0u);
         }
         __pipeline_commit();
     };
