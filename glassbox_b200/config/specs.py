@@ -54,6 +54,15 @@ class UnitOffsetRmsNormSpec:
 
 
 @dataclass(frozen=True)
+class LayerNormSpec:
+    """Layer norm with a weight and (``bias`` True) a bias: (x - mean) / sqrt(var + eps) * w + b, var the mean of the
+    squared deviations."""
+    eps: float
+    bias: bool = True
+    kind: str = "layernorm"
+
+
+@dataclass(frozen=True)
 class GqaAttentionSpec:
     """Causal grouped-query attention over a paged key/value cache.
 
@@ -107,6 +116,53 @@ class ChannelDeltaSpec:
     gate_rank: int
     norm_eps: float
     kind: str = "channel_delta"
+
+
+@dataclass(frozen=True)
+class SigmoidAttentionSpec:
+    """Causal grouped-query attention whose weights are not a softmax: a visible key weighs sigmoid(q.k * scale + b_head),
+    on its own, with a learned number ``b_head`` per query head (``head_bias``). Queries and keys have ``head_dim``
+    channels and are RMS-normed per head (``qk_norm_eps``; None: no norm; one gain for all query heads, one for all key
+    heads) before ``position`` rotates them; values have ``value_dim`` channels. ``window`` as in ``GqaAttentionSpec``."""
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float
+    position: Any
+    window: Optional[int] = None
+    qk_norm_eps: Optional[float] = None
+    head_bias: bool = True
+    kind: str = "sigmoid_attention"
+
+
+@dataclass(frozen=True)
+class MinGruSpec:
+    """minGRU: per channel S_t = (1 - z_t) S_(t-1) + z_t c_t with the gate z_t = sigmoid(W_z h + b_z) and the candidate c_t
+    from u = W_x h + b_x (u + 1/2 where u >= 0, sigmoid(u) elsewhere), both functions of the current token alone; the
+    output is W_o (S_t * silu(W_g h)). ``width`` channels; the state is float32 and starts at zero."""
+    width: int
+    kind: str = "mingru"
+
+
+@dataclass(frozen=True)
+class RoutedExpertsSpec:
+    """A mixture of ``num_experts`` squared-ReLU feed-forwards of ``expert_size`` hidden units, of which a token uses
+    ``top_k``. Scores are sigmoid(router logits) (float32); the choice is made by score + a stored correction
+    (``correction`` True), the weights are the chosen scores times ``route_scale``, not renormalised. With ``num_groups``
+    > 1 the experts form that many equal runs of neighbours, a run scores the sum of its two best choice scores, and only
+    experts of the ``keep_groups`` best runs can be chosen. ``shared_size`` > 0 adds one expert of that size that every
+    token uses, times sigmoid(w_gate . h) when ``shared_gate`` is True."""
+    num_experts: int
+    top_k: int
+    expert_size: int
+    route_scale: float = 1.0
+    num_groups: int = 1
+    keep_groups: int = 1
+    correction: bool = True
+    shared_size: int = 0
+    shared_gate: bool = True
+    kind: str = "routed_experts"
 
 
 @dataclass(frozen=True)
@@ -168,6 +224,10 @@ class LayerSpec:
     #: x += post(ffn(norm(x))); there ``ffn`` may be None (a layer without a feed-forward)
     mixer_post_norm: Any = None
     ffn_post_norm: Any = None
+    #: "hyper_connections": the residual is ``streams`` rows per token; each branch reads a learned mix of them through
+    #: its norm and its output comes back into all of them through a learned matrix (``ModelConfig.residual_streams`` says
+    #: the same number for the whole model); ``ffn`` may be None
+    streams: int = 0
 
 
 @dataclass(frozen=True)
@@ -197,6 +257,9 @@ class ModelConfig:
     raw: dict = field(default_factory=dict, compare=False, hash=False)
     embedding: Any = EmbeddingSpec()
     head: Any = LmHeadSpec()
+    #: 0: one residual row per token. s >= 1: the residual is s rows per token, all equal to the embedding's output at
+    #: the start and summed in front of the final norm; every layer then has the arrangement "hyper_connections"
+    residual_streams: int = 0
 
     @property
     def num_cache_layers(self) -> int:
@@ -205,6 +268,11 @@ class ModelConfig:
     def validate(self) -> None:
         if not self.layers:
             raise ConfigError("a model needs at least one layer")
+        for i, layer in enumerate(self.layers):
+            if (layer.arrangement == "hyper_connections") != (self.residual_streams > 0) or \
+                    (self.residual_streams > 0 and layer.streams != self.residual_streams):
+                raise ConfigError(f"layer {i}: a model with {self.residual_streams} residual streams needs every layer wired "
+                                  "for exactly that many (arrangement 'hyper_connections'), and no other model has such layers")
         writers = {}
         for i, run in enumerate(self.schedule):
             if not 0 <= run.layer < len(self.layers):

@@ -1,0 +1,146 @@
+// Layer norm with weight and bias, and a residual that is kept as several streams (hyper-connections), in one row kernel.
+//
+// A model with S residual streams keeps, per token, S rows x_1 .. x_S of d float32 numbers (xs [n, S, d]). A sublayer reads
+// one mix of them, u = sum_s read[s] * x_s, through a layer norm, and its output y comes back into all of them at once:
+// x_t <- sum_s mix[s, t] * x_s + write[t] * y. One block per row does, as far as it is asked to:
+//   1. fold in the output y of the sublayer before (new streams from the old ones; stored unless rows are gathered),
+//   2. form u (read == nullptr: the plain sum of the streams; with S == 1 that is the row itself),
+//   3. store u as float32 and / or its layer norm (u - mean) / sqrt(var + eps) * w + b in the activation dtype,
+// so a chain of sublayers costs one launch per sublayer for everything between the products, and the same kernel is the
+// plain layer norm of a model with one residual row (S = 1, nothing to fold in). var is the mean of the squared
+// deviations from the mean (two passes over the row, which lives in shared memory meanwhile). Everything is float32.
+#include "common.cuh"
+
+constexpr int RS_THREADS = 256;
+constexpr int RS_MAX_STREAMS = 8;
+
+__device__ __forceinline__ float rs_block_sum(float v, float* partial) {
+    v = gb_warp_sum(v);
+    __syncthreads();                                  // (partial may still be read from the round before)
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < RS_THREADS / 32; ++w) t += partial[w];
+    return t;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(RS_THREADS) streams_step_kernel(
+    float* __restrict__ xs, int S, int d, const float* __restrict__ y, long long ldy, const float* __restrict__ mix,
+    const float* __restrict__ write, const float* __restrict__ read, const float* __restrict__ w, const float* __restrict__ b,
+    float eps, T* __restrict__ h, float* __restrict__ u_out, const int* __restrict__ rows, const int* __restrict__ positions,
+    int n_out, int n_src) {
+    extern __shared__ __align__(16) float rs_u[];     // the row u, d numbers
+    __shared__ float partial[RS_THREADS / 32];
+    __shared__ float coef[RS_MAX_STREAMS * RS_MAX_STREAMS + 2 * RS_MAX_STREAMS];
+    // (weights of the model: nothing of the step writes them, so they may be read before the wait)
+    if (threadIdx.x < S * S) coef[threadIdx.x] = mix ? mix[threadIdx.x] : 0.f;
+    if (threadIdx.x < S) {
+        coef[RS_MAX_STREAMS * RS_MAX_STREAMS + threadIdx.x] = write ? write[threadIdx.x] : 0.f;
+        coef[RS_MAX_STREAMS * RS_MAX_STREAMS + RS_MAX_STREAMS + threadIdx.x] = read ? read[threadIdx.x] : 1.f;
+    }
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    const int r = blockIdx.x;
+    if (r >= n_out) return;
+    const int src = rows ? rows[r] : r;
+    if (src < 0 || src >= n_src) return;
+    if (!rows && positions && positions[src] < 0) return;      // a padding row of a fixed-shape batch
+    __syncthreads();
+    const float* cm = coef;
+    const float* cw = coef + RS_MAX_STREAMS * RS_MAX_STREAMS;
+    const float* cr = cw + RS_MAX_STREAMS;
+    float* row = xs + (size_t)src * S * d;
+    const bool fold = y != nullptr, keep = fold && rows == nullptr;
+    float total = 0.f;
+    for (int j = threadIdx.x; j < d; j += RS_THREADS) {
+        float v[RS_MAX_STREAMS];
+#pragma unroll
+        for (int s = 0; s < RS_MAX_STREAMS; ++s) v[s] = s < S ? row[(size_t)s * d + j] : 0.f;
+        if (fold) {
+            const float yj = y[(size_t)src * ldy + j];
+            float nv[RS_MAX_STREAMS];
+#pragma unroll
+            for (int t = 0; t < RS_MAX_STREAMS; ++t) {
+                float a = 0.f;
+                if (t < S) {
+#pragma unroll
+                    for (int s = 0; s < RS_MAX_STREAMS; ++s)
+                        if (s < S) a = fmaf(cm[s * S + t], v[s], a);
+                    a = fmaf(cw[t], yj, a);
+                    if (keep) row[(size_t)t * d + j] = a;
+                }
+                nv[t] = a;
+            }
+#pragma unroll
+            for (int s = 0; s < RS_MAX_STREAMS; ++s) v[s] = nv[s];
+        }
+        float u = 0.f;
+#pragma unroll
+        for (int s = 0; s < RS_MAX_STREAMS; ++s)
+            if (s < S) u = fmaf(cr[s], v[s], u);
+        rs_u[j] = u;
+        total += u;
+        if (u_out) u_out[(size_t)r * d + j] = u;
+    }
+    if (h == nullptr) return;
+    const float mean = rs_block_sum(total, partial) / (float)d;
+    float dev = 0.f;
+    for (int j = threadIdx.x; j < d; j += RS_THREADS) {     // (each thread reads back what it wrote itself)
+        const float c = rs_u[j] - mean;
+        dev = fmaf(c, c, dev);
+    }
+    const float rstd = 1.0f / sqrtf(rs_block_sum(dev, partial) / (float)d + eps);
+    T* dst = h + (size_t)r * d;
+    for (int j = threadIdx.x; j < d; j += RS_THREADS)
+        dst[j] = gb_from_float<T>((rs_u[j] - mean) * rstd * w[j] + (b ? b[j] : 0.f));
+}
+
+// xs[r, s, :] = x[r, :] for every stream s: the streams all start as the embedding's output.
+__global__ void __launch_bounds__(256) streams_broadcast_kernel(const float* __restrict__ x, float* __restrict__ xs, long long n,
+                                                                int S, int d) {
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    const long long total = n * d;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+        const long long r = idx / d;
+        const int j = (int)(idx % d);
+        const float v = x[idx];
+        for (int s = 0; s < S; ++s) xs[(r * S + s) * d + j] = v;
+    }
+}
+
+GB_EXPORT int gb_streams_broadcast(const float* x, float* xs, int n, int S, int d, cudaStream_t stream) {
+    GB_REQUIRE(n >= 0 && S >= 1 && d > 0, "gb_streams_broadcast: bad sizes");
+    if (n == 0) return 0;
+    long long total = (long long)n * d;
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    gb_launch(GB_PDL_ELEMENTWISE, streams_broadcast_kernel, dim3(blocks), dim3(256), 0, stream, x, xs, (long long)n, S, d);
+    return gb_check_launch("gb_streams_broadcast");
+}
+
+GB_EXPORT int gb_streams_step(float* xs, int S, int d, const float* y, long long ldy, const float* mix, const float* write,
+                              const float* read, const float* w, const float* b, float eps, void* h, int h_dtype, float* u_out,
+                              const int* rows, const int* positions, int n_out, int n_src, cudaStream_t stream) {
+    GB_REQUIRE(S >= 1 && S <= RS_MAX_STREAMS, "gb_streams_step: %d streams, at most %d are supported", S, RS_MAX_STREAMS);
+    GB_REQUIRE(n_out >= 0 && n_src >= 0 && d > 0 && (size_t)d * 4 <= 160 * 1024, "gb_streams_step: bad sizes (d=%d)", d);
+    GB_REQUIRE(y == nullptr || (mix != nullptr && write != nullptr), "gb_streams_step: folding in an output needs mix and write");
+    GB_REQUIRE(h == nullptr || w != nullptr, "gb_streams_step: a norm needs its weight");
+    if (n_out == 0) return 0;
+    const size_t smem = (size_t)d * 4;
+    if (h == nullptr || h_dtype == GB_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(streams_step_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        gb_launch(GB_PDL_ELEMENTWISE, streams_step_kernel<float>, dim3(n_out), dim3(RS_THREADS), smem, stream, xs, S, d, y, ldy, mix,
+                  write, read, w, b, eps, (float*)h, u_out, rows, positions, n_out, n_src);
+    } else if (h_dtype == GB_BF16) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(streams_step_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        gb_launch(GB_PDL_ELEMENTWISE, streams_step_kernel<__nv_bfloat16>, dim3(n_out), dim3(RS_THREADS), smem, stream, xs, S, d, y, ldy,
+                  mix, write, read, w, b, eps, (__nv_bfloat16*)h, u_out, rows, positions, n_out, n_src);
+    } else {
+        GB_REQUIRE(false, "gb_streams_step: unsupported output dtype %d", h_dtype);
+    }
+    return gb_check_launch("gb_streams_step");
+}

@@ -1,0 +1,225 @@
+// Attention without a softmax over the paged cache: the weight of a visible key is sigmoid(q.k * scale + bias[head]),
+// on its own, not normalised over the keys; out = sum over visible keys of weight * v. A row at position p of its request
+// sees keys max(0, p - window + 1) .. p (window 0: all of them). Query heads share key/value heads in groups. The key
+// size (dim) and the value size (vdim) may differ. Scores, weights and sums are float32.
+//
+//   qk_norm_rope_write   per row: RMS norm of every query and key head over dim (one gain for all query heads, one for
+//                        all key heads, eps inside the root), rotation of the first `rot` channels in neighbouring pairs
+//                        (2i, 2i+1) by the angle float32(position) * inv_freq[i], q to the query buffer, k and v into the
+//                        cache at the row's slot. Input: the float32 sums of the stacked projection q | k | v.
+//   sigmoid_attention_rows  one warp per (row, head), any row (prompt portion or single token), both dtypes: 32 keys at a
+//                        time from the first visible one, a lane per key for the scores, a lane per channel for the sum.
+#include "common.cuh"
+
+constexpr int SA_MAX_DIM = 256;
+constexpr int SA_WARPS = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(128) qk_norm_rope_write_kernel(
+    const float* __restrict__ qkv, long long ld, const float* __restrict__ q_gain, const float* __restrict__ k_gain,
+    const float* __restrict__ inv_freq, const int* __restrict__ positions, const int* __restrict__ slots, T* __restrict__ q_out,
+    T* __restrict__ kcache, T* __restrict__ vcache, int n, int H, int G, int D, int V, int rot, float eps, int page_size,
+    long long num_slots, int write_kv, int* __restrict__ status) {
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    const int row = blockIdx.x;
+    if (row >= n) return;
+    const int pos = positions[row];
+    if (pos < 0) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const float* src = qkv + (size_t)row * ld;
+    long long slot = slots[row];
+    bool store = write_kv != 0;
+    if (store && (slot < 0 || slot >= num_slots)) {
+        if (threadIdx.x == 0) atomicOr(status, GB_STATUS_BAD_SLOT);
+        store = false;
+    }
+    const long long page = slot / page_size;
+    const int off = (int)(slot % page_size);
+    const int pairs = D / 2;          // (an odd last channel is handled apart)
+    for (int head = warp; head < H + G; head += warps) {
+        const bool is_q = head < H;
+        if (!is_q && !store) continue;
+        const float* x = src + (size_t)head * D;     // q heads, then k heads: contiguous in the stacked row
+        const float* gain = is_q ? q_gain : k_gain;      // nullptr: the heads are not normed
+        float r = 1.f;
+        if (gain != nullptr) {
+            float ss = 0.f;
+            for (int i = lane; i < D; i += 32) ss = fmaf(x[i], x[i], ss);
+            ss = gb_warp_sum(ss);
+            r = 1.0f / sqrtf(ss / (float)D + eps);
+        }
+        T* dst = is_q ? q_out + ((size_t)row * H + head) * D
+                      : kcache + ((page * G + (head - H)) * page_size + off) * D;
+        for (int i = lane; i < pairs; i += 32) {
+            float a = x[2 * i] * r, c = x[2 * i + 1] * r;
+            if (gain != nullptr) {
+                a *= gain[2 * i];
+                c *= gain[2 * i + 1];
+            }
+            if (2 * i + 1 < rot) {
+                float sn, cs;
+                sincosf((float)pos * inv_freq[i], &sn, &cs);
+                const float ra = a * cs - c * sn, rc = c * cs + a * sn;
+                a = ra;
+                c = rc;
+            }
+            dst[2 * i] = gb_from_float<T>(a);
+            dst[2 * i + 1] = gb_from_float<T>(c);
+        }
+        if ((D & 1) && lane == 0) dst[D - 1] = gb_from_float<T>(x[D - 1] * r * (gain ? gain[D - 1] : 1.f));
+    }
+    if (store) {
+        const float* v = src + (size_t)(H + G) * D;
+        for (int idx = threadIdx.x; idx < G * V; idx += blockDim.x) {
+            const int g = idx / V, i = idx % V;
+            vcache[((page * G + g) * page_size + off) * V + i] = gb_from_float<T>(v[idx]);
+        }
+    }
+}
+
+GB_EXPORT int gb_qk_norm_rope_write(const float* qkv, long long ld, const float* q_gain, const float* k_gain, const float* inv_freq,
+                                    const int* positions, const int* slots, void* q_out, void* kcache, void* vcache, int dtype, int n,
+                                    int H, int G, int D, int V, int rot, float eps, int page_size, long long num_slots, int write_kv,
+                                    int* status, cudaStream_t stream) {
+    GB_REQUIRE(n >= 0 && H > 0 && G > 0 && D > 0 && V > 0, "gb_qk_norm_rope_write: bad sizes");
+    GB_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= D, "gb_qk_norm_rope_write: %d rotated channels of %d", rot, D);
+    GB_REQUIRE(rot == 0 || inv_freq != nullptr, "gb_qk_norm_rope_write: a rotation needs its frequencies");
+    if (n == 0) return 0;
+    if (dtype == GB_F32)
+        gb_launch(GB_PDL_ELEMENTWISE, qk_norm_rope_write_kernel<float>, dim3(n), dim3(128), 0, stream, qkv, ld, q_gain, k_gain, inv_freq,
+                  positions, slots, (float*)q_out, (float*)kcache, (float*)vcache, n, H, G, D, V, rot, eps, page_size, num_slots,
+                  write_kv, status);
+    else if (dtype == GB_BF16)
+        gb_launch(GB_PDL_ELEMENTWISE, qk_norm_rope_write_kernel<__nv_bfloat16>, dim3(n), dim3(128), 0, stream, qkv, ld, q_gain, k_gain,
+                  inv_freq, positions, slots, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, n, H, G, D, V,
+                  rot, eps, page_size, num_slots, write_kv, status);
+    else
+        GB_REQUIRE(false, "gb_qk_norm_rope_write: unsupported dtype %d", dtype);
+    return gb_check_launch("gb_qk_norm_rope_write");
+}
+
+// q . k over D channels; q in shared memory as float32, k a row of the cache.
+template <typename T>
+__device__ __forceinline__ float sa_dot(const float* __restrict__ q, const T* __restrict__ k, int D);
+
+template <>
+__device__ __forceinline__ float sa_dot<float>(const float* __restrict__ q, const float* __restrict__ k, int D) {
+    float d = 0.f;
+    if (D % 4 == 0 && ((uintptr_t)k & 15) == 0) {
+        for (int i = 0; i < D; i += 4) {
+            const float4 kv = *reinterpret_cast<const float4*>(k + i);
+            d = fmaf(q[i], kv.x, d); d = fmaf(q[i + 1], kv.y, d); d = fmaf(q[i + 2], kv.z, d); d = fmaf(q[i + 3], kv.w, d);
+        }
+    } else {
+        for (int i = 0; i < D; ++i) d = fmaf(q[i], k[i], d);
+    }
+    return d;
+}
+
+template <>
+__device__ __forceinline__ float sa_dot<__nv_bfloat16>(const float* __restrict__ q, const __nv_bfloat16* __restrict__ k, int D) {
+    float d = 0.f;
+    if (D % 8 == 0 && ((uintptr_t)k & 15) == 0) {
+        for (int i = 0; i < D; i += 8) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(k + i);
+            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const float2 f = __bfloat1622float2(p[t]);
+                d = fmaf(q[i + 2 * t], f.x, d);
+                d = fmaf(q[i + 2 * t + 1], f.y, d);
+            }
+        }
+    } else {
+        for (int i = 0; i < D; ++i) d = fmaf(q[i], __bfloat162float(k[i]), d);
+    }
+    return d;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(SA_WARPS * 32) sigmoid_attention_rows_kernel(
+    const T* __restrict__ q, T* __restrict__ out, const T* __restrict__ kcache, const T* __restrict__ vcache,
+    const int* __restrict__ block_tables, int max_pages, const int* __restrict__ row_seq, const int* __restrict__ positions,
+    const float* __restrict__ head_bias, int n, int H, int G, int D, int V, int page_size, long long num_pages, float scale,
+    int window, int* __restrict__ status) {
+    __shared__ float qs[SA_WARPS][SA_MAX_DIM];
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long task = (long long)blockIdx.x * SA_WARPS + warp;
+    if (task >= (long long)n * H) return;
+    const int row = (int)(task / H), head = (int)(task % H);
+    const int g = head / (H / G);
+    int pos = positions[row];
+    if (pos < 0) return;
+    if (pos / page_size >= max_pages) {      // a position the block table does not reach: reported, the row reads nothing
+        if (lane == 0) atomicOr(status, GB_STATUS_BAD_POSITION);
+        return;
+    }
+    const int* table = block_tables + (size_t)row_seq[row] * max_pages;
+    const T* qrow = q + ((size_t)row * H + head) * D;
+    for (int i = lane; i < D; i += 32) qs[warp][i] = gb_to_float(qrow[i]);
+    __syncwarp();
+    const float bias = head_bias ? head_bias[head] : 0.f;
+    const int first = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+    float acc[SA_MAX_DIM / 32];
+#pragma unroll
+    for (int j = 0; j < SA_MAX_DIM / 32; ++j) acc[j] = 0.f;
+    for (int base = first; base <= pos; base += 32) {
+        const int key = base + lane;
+        float p = 0.f;
+        long long at = -1;                   // (page * G + g) * page_size + offset of this lane's key
+        if (key <= pos) {
+            const long long page = table[key / page_size];
+            if (page < 0 || page >= num_pages) {
+                atomicOr(status, GB_STATUS_BAD_SLOT);
+            } else {
+                at = (page * G + g) * page_size + key % page_size;
+                const float s = sa_dot<T>(qs[warp], kcache + at * D, D) * scale + bias;
+                p = 1.0f / (1.0f + expf(-s));
+            }
+        }
+        const int count = min(32, pos - base + 1);
+        for (int t = 0; t < count; ++t) {
+            const float pt = __shfl_sync(0xffffffffu, p, t);
+            const long long vr = __shfl_sync(0xffffffffu, at, t);
+            if (vr < 0) continue;
+            const T* vp = vcache + vr * V;
+#pragma unroll
+            for (int j = 0; j < SA_MAX_DIM / 32; ++j) {
+                const int i = lane + 32 * j;
+                if (i < V) acc[j] = fmaf(pt, gb_to_float(vp[i]), acc[j]);
+            }
+        }
+    }
+    T* orow = out + ((size_t)row * H + head) * V;
+#pragma unroll
+    for (int j = 0; j < SA_MAX_DIM / 32; ++j) {
+        const int i = lane + 32 * j;
+        if (i < V) orow[i] = gb_from_float<T>(acc[j]);
+    }
+}
+
+GB_EXPORT int gb_sigmoid_attention_rows(const void* q, void* out, int dtype, const void* kcache, const void* vcache,
+                                        const int* block_tables, int max_pages, const int* row_seq, const int* positions,
+                                        const float* head_bias, int n, int H, int G, int D, int V, int page_size, long long num_pages,
+                                        float scale, int window, int* status, cudaStream_t stream) {
+    GB_REQUIRE(n >= 0 && H > 0 && G > 0 && H % G == 0, "gb_sigmoid_attention_rows: heads %d must be a multiple of kv heads %d", H, G);
+    GB_REQUIRE(D > 0 && D <= SA_MAX_DIM && V > 0 && V <= SA_MAX_DIM, "gb_sigmoid_attention_rows: head sizes %d / %d are outside 1..%d",
+               D, V, SA_MAX_DIM);
+    GB_REQUIRE(page_size > 0 && max_pages > 0 && window >= 0, "gb_sigmoid_attention_rows: bad page geometry or window");
+    if (n == 0) return 0;
+    const int blocks = gb_ceil_div((long long)n * H, SA_WARPS);
+    if (dtype == GB_F32)
+        gb_launch(GB_PDL_ATTENTION, sigmoid_attention_rows_kernel<float>, dim3(blocks), dim3(SA_WARPS * 32), 0, stream, (const float*)q,
+                  (float*)out, (const float*)kcache, (const float*)vcache, block_tables, max_pages, row_seq, positions, head_bias, n, H,
+                  G, D, V, page_size, num_pages, scale, window, status);
+    else if (dtype == GB_BF16)
+        gb_launch(GB_PDL_ATTENTION, sigmoid_attention_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(SA_WARPS * 32), 0, stream,
+                  (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_tables,
+                  max_pages, row_seq, positions, head_bias, n, H, G, D, V, page_size, num_pages, scale, window, status);
+    else
+        GB_REQUIRE(false, "gb_sigmoid_attention_rows: unsupported dtype %d", dtype);
+    return gb_check_launch("gb_sigmoid_attention_rows");
+}

@@ -127,6 +127,9 @@ class StepContext:
         self.prepared_norm = None         # parts.base.PreparedNorm: what the last such product left for that norm
         # A wiring that norms a branch before it joins the residual hands the part a blank buffer instead of the residual:
         self.overwrite_output = False     # True: the part's last product stores into the tensor it was given, not adds
+        # A wiring over several residual streams leaves the fold of a branch's output into the streams to the kernel
+        # that reads the streams next: (y, mix, write), see parts/block.py
+        self.pending_fold = None
 
     def scratch(self, name: str, shape, dtype: Optional[torch.dtype] = None, grow: bool = False) -> torch.Tensor:
         return (self._grow if grow else self._scratch).get(name, shape, dtype, grow)

@@ -14,6 +14,7 @@ import torch
 from .. import kernels
 from ..config.specs import ModelConfig
 from ..parts import build_block, build_part
+from ..parts.block import collapse_streams
 from ..parts.base import Mixer, Part
 from ..weights.binding import ParamSpec
 
@@ -116,8 +117,14 @@ class DecoderModel:
 
     def _forward(self, ctx, x, in_program: bool) -> torch.Tensor:
         n, d = ctx.n, self.config.hidden_size
-        ctx.next_norm = ctx.norm_after_layer = ctx.prepared_norm = None
+        ctx.next_norm = ctx.norm_after_layer = ctx.prepared_norm = ctx.pending_fold = None
         self.embed.forward(ctx, ctx.tokens, x)
+        streams = self.config.residual_streams
+        if streams:
+            # the residual is several rows per token, all equal to the embedding's output at the start; the layers
+            # work on them and the final norm reads their sum
+            embedded, x = x, ctx.scratch("x_streams", (n, streams * d), torch.float32)
+            kernels.streams_broadcast(embedded, x, streams)
         schedule = self.config.schedule
         # (a program's persistent kernel asks for the next layer's keys and values itself)
         side = ctx.side_stream if ctx.decode_only and not in_program else None
@@ -150,6 +157,9 @@ class DecoderModel:
         logits = ctx.scratch("logits", (w, self.config.vocab_size), torch.float32, grow=True)
         if w:
             hs = ctx.scratch("hs", (w, d))
-            self.final_norm.forward(ctx, x, hs, rows=ctx.want_rows)
+            if streams:
+                collapse_streams(ctx, x, streams, self.final_norm, hs, rows=ctx.want_rows)
+            else:
+                self.final_norm.forward(ctx, x, hs, rows=ctx.want_rows)
             self.head.forward(ctx, hs, logits)
         return logits

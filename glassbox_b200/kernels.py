@@ -92,6 +92,14 @@ _SIGNATURES = {
     "gb_channel_delta_decode": [_P, _LL, _P, _LL, _P, _LL, _P, _P, _P, _LL, _P, _LL, _P, _F, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I,
                                 _I, _I, _P, _P, _LL, _P, _LL, _I, _I, _I, _I, _P, _P, _I, _P],
     "gb_short_conv_state": [_P, _LL, _P, _LL, _LL, _P, _P, _P, _I, _I, _I, _I, _P],
+    "gb_streams_broadcast": [_P, _P, _I, _I, _I, _P],
+    "gb_streams_step": [_P, _I, _I, _P, _LL, _P, _P, _P, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _P],
+    "gb_qk_norm_rope_write": [_P, _LL, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _LL, _I, _P, _P],
+    "gb_sigmoid_attention_rows": [_P, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
+    "gb_mingru_scan": [_P, _LL, _P, _P, _P, _LL, _LL, _P, _LL, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P],
+    "gb_moe_route": [_P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P, _P, _P],
+    "gb_moe_expert_rows": [_P, _I, _I, _P, _P, _I, _P, _P, _I, _I, _I, _P, _P],
+    "gb_moe_combine": [_P, _P, _I, _P, _LL, _P, _P, _P, _LL, _I, _I, _I, _P],
     "gb_program_op_bytes": [],
     "gb_program_max_rows": [],
 }
@@ -1072,3 +1080,143 @@ def short_conv_state(x: torch.Tensor, state: torch.Tensor, state_off: int, taps:
     assert state_off + (taps - 1) * C <= state.shape[1]
     _call("gb_short_conv_state", _ptr(x), x.stride(0), _ptr(state), state.stride(0), state_off, _ptr(seq_first_row),
           _ptr(seq_start_pos), _ptr(seq_slots), seq_start_pos.shape[0], C, taps, state.shape[0], _stream())
+
+
+# ------------------------------------------------------------------- layer norm and a residual kept as several streams
+def streams_broadcast(x: torch.Tensor, xs: torch.Tensor, streams: int) -> None:
+    """xs[r, s, :] = x[r, :] for every stream s; float32."""
+    _cuda(x, xs)
+    n, d = x.shape
+    assert x.dtype == xs.dtype == torch.float32 and x.is_contiguous() and xs.is_contiguous() and xs.shape == (n, streams * d)
+    _call("gb_streams_broadcast", _ptr(x), _ptr(xs), n, streams, d, _stream())
+
+
+def streams_step(xs: torch.Tensor, streams: int, *, fold=None, read: Optional[torch.Tensor] = None, norm=None,
+                 h: Optional[torch.Tensor] = None, u_out: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
+                 positions: Optional[torch.Tensor] = None) -> None:
+    """One pass over the rows of a residual kept as ``streams`` rows per token (xs float32 [n, streams * d]; one stream: the
+    plain residual). ``fold`` = (y, mix, write): first x_t <- sum_s mix[s, t] x_s + write[t] * y for all streams at once (y
+    float32 [n, d]; stored back unless ``rows`` gathers). Then u = sum_s read[s] x_s (``read`` None: the plain sum), stored
+    as float32 into ``u_out`` and / or through the layer norm ``norm`` = (weight, bias or None, eps) into ``h`` (any
+    activation dtype). ``rows`` (int32) picks the input row of each output row; ``positions`` marks padding rows (< 0),
+    which are skipped."""
+    _cuda(xs, read, h, u_out, rows, positions)
+    n_src = xs.shape[0]
+    d = xs.shape[1] // streams
+    assert xs.dtype == torch.float32 and xs.is_contiguous() and xs.shape[1] == streams * d
+    n_out = rows.shape[0] if rows is not None else n_src
+    y = mix = write = None
+    if fold is not None:
+        y, mix, write = fold
+        assert y.dtype == mix.dtype == write.dtype == torch.float32 and y.shape == (n_src, d) and y.stride(1) == 1
+        assert mix.numel() == streams * streams and write.numel() == streams and mix.is_contiguous()
+    w = b = None
+    eps = 0.0
+    if h is not None:
+        w, b, eps = norm
+        assert h.shape == (n_out, d) and h.is_contiguous() and w.dtype == torch.float32 and w.numel() == d
+        assert b is None or (b.dtype == torch.float32 and b.numel() == d)
+    assert read is None or (read.dtype == torch.float32 and read.numel() == streams)
+    assert u_out is None or (u_out.dtype == torch.float32 and u_out.shape == (n_out, d) and u_out.is_contiguous())
+    _call("gb_streams_step", _ptr(xs), streams, d, _ptr(y), y.stride(0) if y is not None else 0, _ptr(mix), _ptr(write), _ptr(read),
+          _ptr(w), _ptr(b), float(eps), _ptr(h), _dt(h) if h is not None else F32, _ptr(u_out), _ptr(rows), _ptr(positions),
+          n_out, n_src, _stream())
+
+
+# ------------------------------------------------------------------------------------ attention without a softmax
+def qk_norm_rope_write(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor],
+                       positions: torch.Tensor, slots: torch.Tensor, q_out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
+                       heads: int, kv_heads: int, dim: int, vdim: int, rot: int, eps: float, page_size: int, write_kv: bool,
+                       status: torch.Tensor) -> None:
+    """From the float32 sums of the stacked projection q | k | v: RMS norm of every query and key head over ``dim`` (one
+    gain for the query heads, one for the key heads; None: no norm), rotation of the first ``rot`` channels in neighbouring pairs by
+    float32(position) * inv_freq[i], q into ``q_out`` [n, heads * dim], k and v into the paged cache at each row's slot."""
+    _cuda(qkv, q_gain, k_gain, inv_freq, positions, slots, q_out, kcache, vcache, status)
+    n = qkv.shape[0]
+    assert qkv.dtype == torch.float32 and qkv.stride(1) == 1 and qkv.shape[1] == (heads + kv_heads) * dim + kv_heads * vdim
+    for gain in (q_gain, k_gain):
+        assert gain is None or (gain.dtype == torch.float32 and gain.numel() == dim)
+    assert q_out.shape == (n, heads * dim) and q_out.is_contiguous() and q_out.dtype == kcache.dtype == vcache.dtype
+    assert kcache.is_contiguous() and vcache.is_contiguous() and kcache.shape[-1] == dim and vcache.shape[-1] == vdim
+    assert rot == 0 or (inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot // 2)
+    _call("gb_qk_norm_rope_write", _ptr(qkv), qkv.stride(0), _ptr(q_gain), _ptr(k_gain), _ptr(inv_freq), _ptr(positions), _ptr(slots),
+          _ptr(q_out), _ptr(kcache), _ptr(vcache), _dt(q_out), n, heads, kv_heads, dim, vdim, rot, float(eps), page_size,
+          kcache.shape[0] * page_size, 1 if write_kv else 0, _ptr(status), _stream())
+
+
+def sigmoid_attention_rows(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
+                           row_seq: torch.Tensor, positions: torch.Tensor, head_bias: Optional[torch.Tensor], heads: int, kv_heads: int,
+                           dim: int, vdim: int, page_size: int, scale: float, window: Optional[int], status: torch.Tensor) -> None:
+    """out[row, head, :] = sum over the row's visible keys of sigmoid(q . k * scale + head_bias[head]) * v: no softmax, the
+    weights are not normalised over the keys. One warp per (row, head); any row, both dtypes."""
+    _cuda(q, out, kcache, vcache, block_tables, row_seq, positions, head_bias, status)
+    n = q.shape[0]
+    assert q.shape == (n, heads * dim) and out.shape == (n, heads * vdim) and q.is_contiguous() and out.is_contiguous()
+    assert q.dtype == out.dtype == kcache.dtype == vcache.dtype and block_tables.is_contiguous()
+    assert head_bias is None or (head_bias.dtype == torch.float32 and head_bias.numel() == heads)
+    _call("gb_sigmoid_attention_rows", _ptr(q), _ptr(out), _dt(q), _ptr(kcache), _ptr(vcache), _ptr(block_tables),
+          block_tables.shape[1], _ptr(row_seq), _ptr(positions), _ptr(head_bias), n, heads, kv_heads, dim, vdim, page_size,
+          kcache.shape[0], float(scale), int(window) if window else 0, _ptr(status), _stream())
+
+
+# ------------------------------------------------------------------------------------------------ minGRU
+def mingru_scan(proj: torch.Tensor, bias_z: torch.Tensor, bias_x: torch.Tensor, state: torch.Tensor, state_off: int, out: torch.Tensor,
+                seq_first_row: torch.Tensor, seq_start_pos: torch.Tensor, seq_slots: torch.Tensor, width: int, write_state: bool,
+                status: torch.Tensor) -> None:
+    """S_t = (1 - z_t) S_(t-1) + z_t c_t along each request's rows, from and to ``width`` float32 numbers at ``state_off``
+    of the request's slot; z = sigmoid(proj[:, :width] + bias_z), c from u = proj[:, width:2 width] + bias_x (u + 1/2 where
+    u >= 0, sigmoid(u) elsewhere), out = S_t * silu(proj[:, 2 width:3 width]). proj float32 (a column slice is allowed)."""
+    _cuda(proj, bias_z, bias_x, state, out, seq_first_row, seq_start_pos, seq_slots, status)
+    n = proj.shape[0]
+    assert proj.dtype == torch.float32 and proj.shape[1] == 3 * width and proj.stride(1) == 1
+    assert bias_z.dtype == bias_x.dtype == state.dtype == torch.float32 and bias_z.numel() == width and bias_x.numel() == width
+    assert state.dim() == 2 and state.is_contiguous() and out.shape == (n, width) and out.stride(1) == 1
+    _call("gb_mingru_scan", _ptr(proj), proj.stride(0), _ptr(bias_z), _ptr(bias_x), _ptr(state), state.stride(0), state_off, _ptr(out),
+          out.stride(0), _dt(out), _ptr(seq_first_row), _ptr(seq_start_pos), _ptr(seq_slots), seq_start_pos.shape[0], width,
+          state.shape[0], 1 if write_state else 0, _ptr(status), _stream())
+
+
+# ------------------------------------------------------------------------------------------- routed experts
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], w_gate: Optional[torch.Tensor],
+              positions: torch.Tensor, top: int, groups: int, keep: int, route_scale: float, choice: torch.Tensor,
+              weight: torch.Tensor, gate: Optional[torch.Tensor]) -> None:
+    """Per row: float32 router logits, sigmoid scores, the ``top`` experts by score + correction among the ``keep`` best of
+    ``groups`` runs of neighbouring experts, weights score * route_scale; ``gate`` = sigmoid(w_gate . h) per row."""
+    _cuda(h, w_router, correction, w_gate, positions, choice, weight, gate)
+    n, d = h.shape
+    E = w_router.shape[0]
+    assert h.is_contiguous() and w_router.dtype == torch.float32 and w_router.shape == (E, d) and w_router.is_contiguous()
+    assert correction is None or (correction.dtype == torch.float32 and correction.numel() == E)
+    assert w_gate is None or (w_gate.dtype == torch.float32 and w_gate.numel() == d and gate is not None)
+    assert choice.dtype == torch.int32 and choice.shape == (n, top) and choice.is_contiguous()
+    assert weight.dtype == torch.float32 and weight.shape == (n, top) and weight.is_contiguous()
+    assert gate is None or (gate.dtype == torch.float32 and gate.numel() >= n)
+    _call("gb_moe_route", _ptr(h), _dt(h), d, _ptr(w_router), _ptr(correction), _ptr(w_gate), _ptr(positions), n, E, top, groups, keep,
+          float(route_scale), _ptr(choice), _ptr(weight), _ptr(gate), _stream())
+
+
+def moe_expert_rows(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, experts: int, choice: torch.Tensor,
+                    positions: torch.Tensor, pair: torch.Tensor) -> None:
+    """pair[row, k, :] = W_down[e] relu(W_up[e] h[row])^2 with e = choice[row, k]; w_up [experts * ff, d] and w_down
+    [experts * d, ff] hold the experts' matrices stacked by rows; one block per (row, k)."""
+    _cuda(h, w_up, w_down, choice, positions, pair)
+    n, d = h.shape
+    top = choice.shape[1]
+    ff = w_up.shape[0] // experts
+    assert h.dtype == w_up.dtype == w_down.dtype and h.is_contiguous() and w_up.is_contiguous() and w_down.is_contiguous()
+    assert w_up.shape == (experts * ff, d) and w_down.shape == (experts * d, ff)
+    assert pair.dtype == torch.float32 and pair.shape == (n, top * d) and pair.is_contiguous()
+    _call("gb_moe_expert_rows", _ptr(h), _dt(h), d, _ptr(w_up), _ptr(w_down), ff, _ptr(choice), _ptr(positions), n, experts, top,
+          _ptr(pair), _stream())
+
+
+def moe_combine(pair: torch.Tensor, weight: torch.Tensor, shared: Optional[torch.Tensor], gate: Optional[torch.Tensor],
+                positions: torch.Tensor, out: torch.Tensor, accumulate: bool) -> None:
+    """out[row] (+)= sum_k weight[row, k] * pair[row, k] + gate[row] * shared[row]; float32, the sums in a fixed order."""
+    _cuda(pair, weight, shared, gate, positions, out)
+    n, d = out.shape
+    top = weight.shape[1]
+    assert pair.dtype == weight.dtype == out.dtype == torch.float32 and pair.shape == (n, top * d) and out.stride(1) == 1
+    assert shared is None or (shared.dtype == torch.float32 and shared.shape == (n, d) and shared.stride(1) == 1)
+    _call("gb_moe_combine", _ptr(pair), _ptr(weight), top, _ptr(shared), shared.stride(0) if shared is not None else 0, _ptr(gate),
+          _ptr(positions), _ptr(out), out.stride(0), n, d, 1 if accumulate else 0, _stream())

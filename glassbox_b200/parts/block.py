@@ -1,14 +1,18 @@
 """A layer: a mixer and a feed-forward wired around the float32 residual stream.
 
 "pre_norm" is x += mixer(norm(x)); x += ffn(norm(x)), with no norms after the parts
-(crates/glassbox-core/src/model.rs:251-348). "sandwich_norm" norms each branch on the way out as well:
-x += post(mixer(norm(x))); x += post(ffn(norm(x))). The arrangement is looked up by name, so another
+(crates/glassbox-core/src/model.rs:251-348; a layer may lack the feed-forward). "sandwich_norm" norms each branch on the
+way out as well: x += post(mixer(norm(x))); x += post(ffn(norm(x))). "hyper_connections" keeps the residual as several
+streams x_1 .. x_S per token: a branch reads u = sum_s read[s] x_s through its norm, and its output y comes back into all
+streams at once, x_t <- sum_s mix[s, t] x_s + write[t] y. The arrangement is looked up by name, so another
 wiring (post-norm, parallel branches) is another registered class.
 """
 from __future__ import annotations
 
 import torch
 
+from .. import kernels
+from ..weights.binding import ParamSpec
 from .base import DeferredNorm, Part, build_part, register_part
 
 
@@ -20,11 +24,16 @@ class PreNormBlock(Part):
         self.hidden_size = hidden_size
         self.mixer_norm = build_part("norm", spec.mixer_norm, hidden_size=hidden_size)
         self.mixer = build_part("mixer", spec.mixer, hidden_size=hidden_size)
-        self.ffn_norm = build_part("norm", spec.ffn_norm, hidden_size=hidden_size)
-        self.ffn = build_part("ffn", spec.ffn, hidden_size=hidden_size)
+        self.ffn = self.ffn_norm = None          # (a layer may be a mixer alone)
+        if spec.ffn is not None:
+            self.ffn_norm = build_part("norm", spec.ffn_norm, hidden_size=hidden_size)
+            self.ffn = build_part("ffn", spec.ffn, hidden_size=hidden_size)
 
     def sub_parts(self):
-        return {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "ffn_norm": self.ffn_norm, "ffn": self.ffn}
+        parts = {"mixer_norm": self.mixer_norm, "mixer": self.mixer}
+        if self.ffn is not None:
+            parts.update({"ffn_norm": self.ffn_norm, "ffn": self.ffn})
+        return parts
 
     def entry_norm(self):
         """The norm that reads the residual first when this layer runs (whoever runs the layer before may tell
@@ -37,13 +46,15 @@ class PreNormBlock(Part):
         ``ctx.norm_after_layer`` (optional) is the norm that will read ``x`` after this layer."""
         after_layer = getattr(ctx, "norm_after_layer", None)
         h = DeferredNorm(ctx, self.mixer_norm, x)
-        ctx.next_norm = self.ffn_norm          # a hint to the product that adds the mixer's output into x
+        # a hint to the product that adds the mixer's output into x
+        ctx.next_norm = self.ffn_norm if self.ffn is not None else after_layer
         self.mixer.forward(ctx, h if self.mixer.accepts_deferred_input else h.tensor(), x, cache, writes_cache)
         if after_mixer is not None:
             after_mixer()
-        h = DeferredNorm(ctx, self.ffn_norm, x)
-        ctx.next_norm = after_layer
-        self.ffn.forward(ctx, h if self.ffn.accepts_deferred_input else h.tensor(), x)
+        if self.ffn is not None:
+            h = DeferredNorm(ctx, self.ffn_norm, x)
+            ctx.next_norm = after_layer
+            self.ffn.forward(ctx, h if self.ffn.accepts_deferred_input else h.tensor(), x)
         ctx.next_norm = None
 
 
@@ -101,6 +112,99 @@ class SandwichNormBlock(Part):
             self._branch(ctx, self.ffn, self.ffn_norm, self.ffn_post_norm, x, lambda h, out: self.ffn.forward(ctx, h, out))
 
 
+class StreamMixing(Part):
+    """The three learned pieces of one branch of a hyper-connection layer over S residual streams: ``read`` [S] (how the
+    branch's input is mixed from the streams), ``write`` [S] (how much of the branch's output each stream takes) and
+    ``mix`` [S, S], indexed [from, to] (how the streams feed one another meanwhile). Float32."""
+    launches_through_kernels_only = True
+
+    def __init__(self, streams: int):
+        super().__init__(None)
+        self.streams = streams
+
+    def param_specs(self):
+        s = self.streams
+        return {"read": ParamSpec((s,), role="gain", init=(1.0 / s, 0.1 / s)), "write": ParamSpec((s,), role="gain", init=(1.0, 0.1)),
+                "mix": ParamSpec((s, s), role="gain", init=(1.0 / s, 0.1 / s))}
+
+
+class HyperConnectionBlock(Part):
+    """A layer over a residual of S streams per token (``xs`` float32 [n, S * d]). For the mixer, then (if the layer has
+    one) the feed-forward: u = sum_s read[s] x_s; y = branch(norm(u)); x_t <- sum_s mix[s, t] x_s + write[t] y for all t
+    at once. A branch gets a float32 buffer for y, as in the sandwich wiring. The fold of y into the streams is not
+    launched here: it is left in ``ctx.pending_fold`` and the kernel that reads the streams next (the next branch's read
+    and norm, in this or the next layer, or the sum in front of the final norm: ``collapse_streams``) performs it on
+    its way, so that a branch costs one launch beside its own."""
+    launches_through_kernels_only = False      # (clearing the buffer for a part that adds is a torch operation)
+
+    def __init__(self, spec, *, hidden_size: int):
+        super().__init__(spec)
+        if spec.streams < 1:
+            raise ValueError("a hyper_connections layer needs at least one residual stream")
+        self.hidden_size, self.streams = hidden_size, spec.streams
+        self.mixer_norm = build_part("norm", spec.mixer_norm, hidden_size=hidden_size)
+        self.mixer = build_part("mixer", spec.mixer, hidden_size=hidden_size)
+        self.mixer_streams = StreamMixing(spec.streams)
+        self.ffn = self.ffn_norm = self.ffn_streams = None
+        if spec.ffn is not None:
+            self.ffn_norm = build_part("norm", spec.ffn_norm, hidden_size=hidden_size)
+            self.ffn = build_part("ffn", spec.ffn, hidden_size=hidden_size)
+            self.ffn_streams = StreamMixing(spec.streams)
+
+    def sub_parts(self):
+        parts = {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "mixer_streams": self.mixer_streams}
+        if self.ffn is not None:
+            parts.update({"ffn_norm": self.ffn_norm, "ffn": self.ffn, "ffn_streams": self.ffn_streams})
+        return parts
+
+    def _branch(self, ctx, part, norm, mixing, xs, run) -> None:
+        n, d = xs.shape[0], self.hidden_size
+        h = ctx.scratch("h", (n, d))
+        fold, ctx.pending_fold = getattr(ctx, "pending_fold", None), None
+        as_ln = getattr(norm, "as_layernorm", None)
+        if as_ln is not None:
+            kernels.streams_step(xs, self.streams, fold=fold, read=mixing.params["read"], norm=as_ln(), h=h, positions=ctx.positions)
+        else:
+            u = ctx.scratch("stream_mix", (n, d), torch.float32)
+            kernels.streams_step(xs, self.streams, fold=fold, read=mixing.params["read"], u_out=u, positions=ctx.positions)
+            norm.forward(ctx, u, h)
+        y = ctx.scratch("branch", (n, d), torch.float32)
+        ctx.overwrite_output = bool(part.can_overwrite_output)
+        if not ctx.overwrite_output:
+            y.zero_()
+        try:
+            run(h, y)
+        finally:
+            ctx.overwrite_output = False
+        ctx.pending_fold = (y, mixing.params["mix"], mixing.params["write"])
+
+    def forward(self, ctx, xs, cache, writes_cache: bool, after_mixer=None) -> None:
+        ctx.next_norm = ctx.prepared_norm = None      # no product of this layer completes residual rows
+        self._branch(ctx, self.mixer, self.mixer_norm, self.mixer_streams, xs,
+                     lambda h, out: self.mixer.forward(ctx, h, out, cache, writes_cache))
+        if after_mixer is not None:
+            after_mixer()
+        if self.ffn is not None:
+            self._branch(ctx, self.ffn, self.ffn_norm, self.ffn_streams, xs, lambda h, out: self.ffn.forward(ctx, h, out))
+
+
+def collapse_streams(ctx, xs, streams: int, norm, out, rows=None, total=None) -> None:
+    """The end of a residual of several streams: out = norm(sum_s x_s) for the rows ``rows`` (all, if None), after whatever
+    fold is still pending. ``total`` (float32, optional) also receives the sum itself."""
+    fold, ctx.pending_fold = getattr(ctx, "pending_fold", None), None
+    as_ln = getattr(norm, "as_layernorm", None) if norm is not None else None
+    if as_ln is not None:
+        kernels.streams_step(xs, streams, fold=fold, norm=as_ln(), h=out, u_out=total, rows=rows)
+        return
+    n_out = rows.shape[0] if rows is not None else xs.shape[0]
+    u = total if total is not None else ctx.scratch("stream_sum", (n_out, xs.shape[1] // streams), torch.float32)
+    kernels.streams_step(xs, streams, fold=fold, u_out=u, rows=rows)
+    if norm is not None:
+        norm.forward(ctx, u, out)
+
+
+register_part("arrangement", "hyper_connections",
+              lambda kind, *, layer_spec, hidden_size: HyperConnectionBlock(layer_spec, hidden_size=hidden_size), replace=True)
 register_part("arrangement", "sandwich_norm",
               lambda kind, *, layer_spec, hidden_size: SandwichNormBlock(layer_spec, hidden_size=hidden_size), replace=True)
 register_part("arrangement", "pre_norm", lambda kind, *, layer_spec, hidden_size: PreNormBlock(layer_spec, hidden_size=hidden_size),

@@ -1,4 +1,4 @@
-"""RMSNorm: out_j = w_j * (x_j / sqrt(mean(x^2) + eps)), statistics in float32, no mean
+"""Norms. RMSNorm: out_j = w_j * (x_j / sqrt(mean(x^2) + eps)), statistics in float32, no mean
 subtraction, no bias, the gain used as stored (crates/glassbox-core/src/model.rs:94-100)."""
 from __future__ import annotations
 
@@ -38,5 +38,30 @@ class UnitOffsetRmsNorm(RmsNorm):
         self.params["weight"] = (self.params["weight"].float() + 1.0).contiguous()
 
 
+class LayerNorm(Norm):
+    """out_j = (x_j - mean) / sqrt(var + eps) * w_j + b_j over a row, var the mean of the squared deviations; statistics
+    and the result in float32, rounded once to the activation dtype. The bias is optional (``spec.bias``)."""
+    launches_through_kernels_only = True
+
+    def __init__(self, spec, *, hidden_size: int):
+        super().__init__(spec)
+        self.eps = float(spec.eps)
+        self.hidden_size = hidden_size
+
+    def param_specs(self):
+        specs = {"weight": ParamSpec((self.hidden_size,), role="gain")}
+        if self.spec.bias:
+            specs["bias"] = ParamSpec((self.hidden_size,), role="gain", init=(0.0, 0.02))
+        return specs
+
+    def as_layernorm(self):
+        """(weight, bias or None, eps): what a kernel that forms the row itself needs to apply this norm on the way."""
+        return self.params["weight"], self.params.get("bias"), self.eps
+
+    def forward(self, ctx, x, out, rows=None) -> None:
+        kernels.streams_step(x, 1, norm=self.as_layernorm(), h=out, rows=rows)
+
+
+register_part("norm", "layernorm", LayerNorm, replace=True)
 register_part("norm", "rmsnorm", RmsNorm, replace=True)
 register_part("norm", "rmsnorm_unit_offset", UnitOffsetRmsNorm, replace=True)

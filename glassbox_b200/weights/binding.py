@@ -22,6 +22,9 @@ class ParamSpec:
     shape: Tuple[int, ...]
     role: str = "matrix"
     pieces: Optional[Tuple[int, ...]] = None
+    #: (mean, standard deviation) of the values that the random-weights mode draws for this parameter, for parameters
+    #: whose role's default (matrices around 0, gains around 1) would make a degenerate model: a bias, a mixing matrix
+    init: Optional[Tuple[float, float]] = None
 
 
 @dataclass(frozen=True)

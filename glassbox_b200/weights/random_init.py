@@ -53,7 +53,9 @@ def random_tensors(raw_config: dict, seed: int, store_dtype: torch.dtype = torch
         for name, r in zip(src.names, rows):
             shape = (r,) + tuple(spec.shape[1:])
             g = _generator(seed, name)
-            if spec.role == "gain":
+            if spec.init is not None and spec.role != "table":
+                t = spec.init[0] + spec.init[1] * torch.randn(shape, generator=g, dtype=torch.float32)
+            elif spec.role == "gain":
                 t = 1.0 + GAIN_STD * torch.randn(shape, generator=g, dtype=torch.float32)
             elif spec.role == "table":
                 t = torch.randint(0, 2 ** 15, shape, generator=g, dtype=torch.int32)
