@@ -416,6 +416,69 @@ def zurerax_workload(args):
     return out
 
 
+# ------------------------------------------------------------------------------------------------ Lonorax beside its neighbours
+#: layer sizes that resemble real models' (random weights): a Lonorax model of three minGRU layers to one sliding-window
+#: sigmoid-attention layer, four residual streams, every feed-forward a mixture of 16 experts (two per token, the best two
+#: of four groups) beside a shared expert: per token as many feed-forward multiply-adds as a dense layer of width ``ff``.
+#: Beside it Zurerax (the framework's other model of recurrent-state and attention layers) and the Llama decoder, both of
+#: the same width, depth and (dense) feed-forward width.
+LONORAX_SIZES = {
+    "w1024": dict(gru=2048, attn=dict(heads=16, kv_heads=4, dim=64, vdim=64), window=1024, rot=32,
+                  moe=dict(experts=16, top=2, ff=1024, groups=(4, 2), shared=2048)),
+    "w2048": dict(gru=4096, attn=dict(heads=32, kv_heads=8, dim=64, vdim=64), window=1024, rot=32,
+                  moe=dict(experts=16, top=2, ff=2048, groups=(4, 2), shared=4096)),
+}
+
+
+def lonorax_raw(size: dict, own: dict) -> dict:
+    from glassbox_b200.models.lonorax import make_lonorax_raw_config
+    layers = []
+    e = own["moe"]
+    for i in range(size["layers"]):
+        mlp = {"kind": "moe", "expert": {"ff": e["ff"]}, "shared": {"ff": e["shared"]},
+               "router": {"experts": e["experts"], "top": e["top"], "scale": 1.0, "groups": {"count": e["groups"][0], "keep": e["groups"][1]}}}
+        if i % 4 == 3:
+            m = dict(own["attn"])
+            m.update(scale=m["dim"] ** -0.5, mask={"size": own["window"]}, rot={"base": 10000.0, "dims": own["rot"]})
+            layers.append({"type": "attention", "mixer": m, "mlp": mlp})
+        else:
+            layers.append({"type": "mingru", "mixer": {"width": own["gru"]}, "mlp": mlp})
+    return make_lonorax_raw_config(vocab=size["vocab"], width=size["width"], layers=layers, streams=4)
+
+
+def lonorax_workload(args):
+    """Prefill and decode throughput of Lonorax models beside Zurerax and the Llama decoder of equal width, depth and
+    feed-forward width; one JSON line. Decode steps end at the context length; three timed regions per point."""
+    T, ctx, K, W = 2048, args.context, min(args.steps, 128), max(args.warmup, 3)
+    out = {"workload": "lonorax", "dtype": args.dtype, "context": ctx, "prefill_tokens": T, "decode_steps": K, "sizes": {}}
+    for name, size in ZURERAX_SIZES.items():
+        row = {}
+        llama = dict(num_hidden_layers=size["layers"], hidden_size=size["width"], intermediate_size=size["ff"],
+                     vocab_size=size["vocab"], rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
+                     max_position_embeddings=8192, **size["llama"])
+        arms = (("lonorax", dict(raw=lonorax_raw(size, LONORAX_SIZES[name]))), ("zurerax", dict(raw=zurerax_raw(size))),
+                ("llama", dict(shape=llama)))
+        for label, kw in arms:
+            if args.only and label not in args.only.split(","):
+                continue
+            mb = ModelBench(f"{label}-{name}", args.dtype, 64, ctx, **kw)
+            try:
+                r = {"weight_mb": round(mb.eng.weight_bytes() / 2 ** 20, 1), "cache_bytes_per_token": mb.eng.cache_bytes_per_token()}
+                times = mb.prefill(T)
+                m, sd = mean_sd(times)
+                r["prefill"] = {"ms": round(m, 3), "sd": round(sd, 3), "tokens_per_s": round(T / (m / 1e3))}
+                for b in (1, 8, 64):
+                    regions, launches, _ = mb.decode(b, K, W, reps=3)
+                    m, sd = mean_sd(regions)
+                    r[f"decode_b{b}"] = {"ms_per_step": round(m / K, 4), "sd": round(sd / K, 4), "tokens_per_s": round(b * K / (m / 1e3)),
+                                         "launches_per_step": round(launches / K, 1)}
+                row[label] = r
+            finally:
+                mb.close()
+        out["sizes"][name] = row
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -430,11 +493,13 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="only the headline region: no other batches, prefill or e2e")
     ap.add_argument("--no-others", action="store_true",
                     help="skip the other model sizes, the serving workload, the 32-bit path and the CPU baseline")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "zurerax"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "zurerax", "lonorax"],
                     help="serving: the mixed workload of the 360M configuration (64 requests, prompts 32-2048, outputs "
                          "32-512, prompt portions of 512, a quarter of the requests sharing a 384-token prefix) through "
                          "the scheduler; prints its own JSON line. zurerax: prefill and decode throughput of Zurerax models "
-                         "at two widths beside the Llama decoder of equal size; prints its own JSON line")
+                         "at two widths beside the Llama decoder of equal size; prints its own JSON line. lonorax: the same for "
+                         "Lonorax models beside Zurerax and Llama of equal size")
+    ap.add_argument("--only", default="", help="with --workload lonorax: the arms to run (lonorax,zurerax,llama), with commas")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -452,6 +517,9 @@ def main():
         return 0
     if args.workload == "zurerax":
         print(json.dumps(zurerax_workload(args)))
+        return 0
+    if args.workload == "lonorax":
+        print(json.dumps(lonorax_workload(args)))
         return 0
     K, W, B, CTX = args.steps, max(args.warmup, 3), args.batch, args.context
     pk = peaks()

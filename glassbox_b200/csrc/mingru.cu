@@ -5,7 +5,7 @@
 // pz | px | pg are the float32 sums of the stacked projection ([n, ld], three blocks of `width` columns), S lives in the
 // request's state slot (float32, `width` numbers from `state_off`), and everything between is float32.
 //
-// mingru_scan_kernel: a block owns MG_CH channels of one request's rows. Its MG_PARTS groups of threads cut the rows into
+// mingru_scan_kernel: a block owns MG_CH channels of one request's rows. Its warps (up to MG_PARTS) cut the rows into
 // consecutive pieces: each group first composes its piece into (A, B) with S_end = A * S_start + B, the pieces' carries
 // are chained in order (a handful of multiply-adds), and a second walk over the piece writes the outputs from the true
 // incoming state. The order of the floating-point operations of a row depends on the length of its portion only through
@@ -13,13 +13,13 @@
 #include "common.cuh"
 
 constexpr int MG_CH = 32;          // channels per block: a warp's lanes
-constexpr int MG_PARTS = 8;        // pieces of the rows: the block's warps
+constexpr int MG_PARTS = 32;       // at most this many pieces of the rows: the block's warps (the launch says how many)
 constexpr int MG_MIN_PIECE = 8;    // shorter portions are walked by fewer groups
 
 __device__ __forceinline__ float mg_sigmoid(float v) { return 1.0f / (1.0f + expf(-v)); }
 
 template <typename T>
-__global__ void __launch_bounds__(MG_CH * MG_PARTS) mingru_scan_kernel(
+__global__ void __launch_bounds__(MG_CH * MG_PARTS) mingru_scan_kernel(     // (blockDim.x / 32 warps = the most pieces)
     const float* __restrict__ proj, long long ld, const float* __restrict__ bz, const float* __restrict__ bx,
     float* __restrict__ state, long long state_stride, long long state_off, T* __restrict__ out, long long ldo,
     const int* __restrict__ seq_first_row, const int* __restrict__ seq_start_pos, const int* __restrict__ seq_slots, int S, int width,
@@ -39,7 +39,8 @@ __global__ void __launch_bounds__(MG_CH * MG_PARTS) mingru_scan_kernel(
     const bool live = ch < width;
     const int r0 = seq_first_row[seq], len = seq_first_row[seq + 1] - r0;
     int parts = (len + MG_MIN_PIECE - 1) / MG_MIN_PIECE;
-    parts = parts < 1 ? 1 : (parts > MG_PARTS ? MG_PARTS : parts);
+    const int most = (int)(blockDim.x >> 5);
+    parts = parts < 1 ? 1 : (parts > most ? most : parts);
     const int piece = (len + parts - 1) / parts;
     const int lo = r0 + part * piece, hi = min(lo + piece, r0 + len);
     const float biasz = live ? bz[ch] : 0.f, biasx = live ? bx[ch] : 0.f;
@@ -84,17 +85,21 @@ __global__ void __launch_bounds__(MG_CH * MG_PARTS) mingru_scan_kernel(
 GB_EXPORT int gb_mingru_scan(const float* proj, long long ld, const float* bz, const float* bx, float* state, long long state_stride,
                              long long state_off, void* out, long long ldo, int out_dtype, const int* seq_first_row,
                              const int* seq_start_pos, const int* seq_slots, int S, int width, int num_slots, int write_state,
-                             int* status, cudaStream_t stream) {
+                             int max_rows, int* status, cudaStream_t stream) {
     GB_REQUIRE(S >= 0 && width > 0 && num_slots > 0, "gb_mingru_scan: bad sizes");
     GB_REQUIRE(state_off >= 0 && state_off + width <= state_stride, "gb_mingru_scan: the state does not fit its slot");
     if (S == 0) return 0;
     dim3 grid(S, gb_ceil_div(width, MG_CH));
+    // as many warps as the longest portion of the step has pieces (the caller's bound on a request's rows in this step)
+    int warps = gb_ceil_div(max_rows > 0 ? max_rows : 1, MG_MIN_PIECE);
+    warps = warps < 1 ? 1 : (warps > MG_PARTS ? MG_PARTS : warps);
+    const dim3 block(MG_CH * warps);
     if (out_dtype == GB_F32)
-        gb_launch(GB_PDL_ELEMENTWISE, mingru_scan_kernel<float>, grid, dim3(MG_CH * MG_PARTS), 0, stream, proj, ld, bz, bx, state,
+        gb_launch(GB_PDL_ELEMENTWISE, mingru_scan_kernel<float>, grid, block, 0, stream, proj, ld, bz, bx, state,
                   state_stride, state_off, (float*)out, ldo, seq_first_row, seq_start_pos, seq_slots, S, width, num_slots, write_state,
                   status);
     else if (out_dtype == GB_BF16)
-        gb_launch(GB_PDL_ELEMENTWISE, mingru_scan_kernel<__nv_bfloat16>, grid, dim3(MG_CH * MG_PARTS), 0, stream, proj, ld, bz, bx, state,
+        gb_launch(GB_PDL_ELEMENTWISE, mingru_scan_kernel<__nv_bfloat16>, grid, block, 0, stream, proj, ld, bz, bx, state,
                   state_stride, state_off, (__nv_bfloat16*)out, ldo, seq_first_row, seq_start_pos, seq_slots, S, width, num_slots,
                   write_state, status);
     else

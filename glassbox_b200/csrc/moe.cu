@@ -259,3 +259,271 @@ GB_EXPORT int gb_moe_combine(const float* pair, const float* weight, int top, co
               ldo, n, d, accumulate);
     return gb_check_launch("gb_moe_combine");
 }
+
+// ----------------------------------------------------------------------------------------------
+// The two halves of moe_expert_rows as kernels of their own, many blocks per (row, choice): the form for a handful of rows
+// (decoding), where one block per pair would leave most of the GPU idle. act float32 [n * top, ff].
+//   up:   act[pair, f]  = relu(W_up[e][f, :] . h[row])^2         grid (pairs, ceil(ff / 8)), a warp per f
+//   down: pair[pair, c] = W_down[e][c, :] . act[pair, :]         grid (pairs, ceil(d / 8)), a warp per c
+// ----------------------------------------------------------------------------------------------
+template <typename T, bool UP>
+__global__ void __launch_bounds__(256) moe_half_rows_kernel(const void* __restrict__ in_, long long ld_in, const T* __restrict__ w, int N,
+                                                            int K, const int* __restrict__ choice, const int* __restrict__ positions,
+                                                            int n, int E, int top, float* __restrict__ out, long long ld_out) {
+    extern __shared__ __align__(16) float moe_smem[];
+    float* x = moe_smem;       // K numbers: the row h (UP) or the pair's activations (DOWN)
+    const int pair = blockIdx.x, row = pair / top;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c = blockIdx.y * 8 + warp;
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();                // (the choice is the router kernel's output: nothing of it may be read before this)
+    const int e = (row < n && positions[row] >= 0) ? choice[pair] : -2;
+    const T* wrow = (e >= 0 && e < E && c < N) ? w + ((size_t)e * N + c) * K : nullptr;
+    if (e == -2) return;
+    if (e < 0 || e >= E) {
+        if (c < N && lane == 0) out[(size_t)pair * ld_out + c] = 0.f;
+        return;
+    }
+    if (UP) {
+        const T* src = (const T*)in_ + (size_t)row * ld_in;
+        for (int i = threadIdx.x; i < K; i += 256) x[i] = gb_to_float(src[i]);
+    } else {
+        const float* src = (const float*)in_ + (size_t)pair * ld_in;
+        for (int i = threadIdx.x; i < K; i += 256) x[i] = src[i];
+    }
+    __syncthreads();
+    if (wrow == nullptr) return;
+    float v = moe_warp_dot<T>(wrow, x, K, lane);
+    if (UP) {
+        v = fmaxf(v, 0.f);
+        v *= v;
+    }
+    if (lane == 0) out[(size_t)pair * ld_out + c] = v;
+}
+
+template <typename T>
+static int moe_half_rows_launch(const void* h, int d, const T* w_up, const T* w_down, int ff, const int* choice, const int* positions,
+                                int n, int E, int top, float* act, float* pair, cudaStream_t stream) {
+    const size_t smem_up = (size_t)d * 4, smem_down = (size_t)ff * 4;
+    if (smem_up > 32 * 1024)
+        cudaFuncSetAttribute(moe_half_rows_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_up);
+    if (smem_down > 32 * 1024)
+        cudaFuncSetAttribute(moe_half_rows_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);
+    gb_launch(GB_PDL_GEMM, moe_half_rows_kernel<T, true>, dim3(n * top, gb_ceil_div(ff, 8)), dim3(256), smem_up, stream, h, (long long)d,
+              w_up, ff, d, choice, positions, n, E, top, act, (long long)ff);
+    int rc = gb_check_launch("gb_moe_expert_halves (up)");
+    if (rc) return rc;
+    gb_launch(GB_PDL_GEMM, moe_half_rows_kernel<T, false>, dim3(n * top, gb_ceil_div(d, 8)), dim3(256), smem_down, stream,
+              (const void*)act, (long long)ff, w_down, d, ff, choice, positions, n, E, top, pair, (long long)d);
+    return gb_check_launch("gb_moe_expert_halves (down)");
+}
+
+GB_EXPORT int gb_moe_expert_halves(const void* h, int dtype, int d, const void* w_up, const void* w_down, int ff, const int* choice,
+                                   const int* positions, int n, int E, int top, float* act, float* pair, cudaStream_t stream) {
+    GB_REQUIRE(n >= 0 && d > 0 && ff > 0 && E > 0 && top > 0, "gb_moe_expert_halves: bad sizes");
+    GB_REQUIRE((size_t)d * 4 <= 200 * 1024 && (size_t)ff * 4 <= 200 * 1024, "gb_moe_expert_halves: rows of %d / %d numbers do not fit", d, ff);
+    if (n == 0) return 0;
+    if (dtype == GB_F32)
+        return moe_half_rows_launch<float>(h, d, (const float*)w_up, (const float*)w_down, ff, choice, positions, n, E, top, act, pair, stream);
+    if (dtype == GB_BF16)
+        return moe_half_rows_launch<__nv_bfloat16>(h, d, (const __nv_bfloat16*)w_up, (const __nv_bfloat16*)w_down, ff, choice, positions,
+                                                   n, E, top, act, pair, stream);
+    GB_REQUIRE(false, "gb_moe_expert_halves: unsupported dtype %d", dtype);
+}
+
+// ----------------------------------------------------------------------------------------------
+// Many rows (prompt portions, large batches), bfloat16: the (row, choice) pairs are sorted by expert, and the experts'
+// products run as ONE grouped product per half on the tensor cores.
+//   moe_sort            one block: counts per expert, where each expert's pairs start (offsets [E + 1]), where its 64-row
+//                       tiles start (tile_start [E + 1]), and sorted[slot] = pair. The order of an expert's pairs is not
+//                       fixed from run to run; no result depends on it (a pair's numbers do not depend on its slot).
+//   moe_grouped_gemm    a block = 64 slots of one expert x 64 outputs, 4 warps of mma.sync m16n8k16 (bf16, float32 sums),
+//                       operands staged by cp.async in two buffers. UP: rows of h gathered by pair, epilogue relu^2, act
+//                       [slot, ff] bfloat16. DOWN: rows of act, float32 out scattered to pair[pair, :].
+// ----------------------------------------------------------------------------------------------
+constexpr int MG_BM = 64, MG_BN = 64, MG_BK = 32, MG_LD = MG_BK + 8;     // (rows padded by 16 bytes: ldmatrix meets no bank twice)
+
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ choice, const int* __restrict__ positions, int n, int E,
+                                                        int top, int* __restrict__ offsets, int* __restrict__ tile_start,
+                                                        int* __restrict__ sorted) {
+    __shared__ int count[MOE_MAX_EXPERTS], cursor[MOE_MAX_EXPERTS];
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    const int pairs = n * top;
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = positions[p / top] >= 0 ? choice[p] : -1;
+        if (e >= 0 && e < E) atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, tiles = 0;
+        for (int e = 0; e < E; ++e) {
+            offsets[e] = at;
+            tile_start[e] = tiles;
+            cursor[e] = at;
+            at += count[e];
+            tiles += (count[e] + MG_BM - 1) / MG_BM;
+        }
+        offsets[E] = at;
+        tile_start[E] = tiles;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = positions[p / top] >= 0 ? choice[p] : -1;
+        if (e >= 0 && e < E) sorted[atomicAdd(&cursor[e], 1)] = p;
+    }
+}
+
+__device__ __forceinline__ void mg_cp_async16(void* smem, const void* gmem, bool valid) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0;        // 0: the 16 bytes are filled with zeros, nothing is read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+
+template <bool UP>
+__global__ void __launch_bounds__(128) moe_grouped_gemm_kernel(const __nv_bfloat16* __restrict__ A, long long lda,
+                                                               const __nv_bfloat16* __restrict__ W, int N, int K,
+                                                               const int* __restrict__ sorted, const int* __restrict__ offsets,
+                                                               const int* __restrict__ tile_start, int E, int top,
+                                                               void* __restrict__ C, long long ldc) {
+    __shared__ __align__(16) __nv_bfloat16 sa[2][MG_BM][MG_LD], sb[2][MG_BN][MG_LD];
+    __shared__ int src_row[MG_BM];           // where each slot's input row is (UP: the token's row; DOWN: the slot), -1: none
+    __shared__ int dst_row[MG_BM];           // where its output goes (UP: the slot; DOWN: the pair)
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    const int tile = blockIdx.x;
+    if (tile >= tile_start[E]) return;
+    int lo = 0, hi = E;                      // the expert whose tiles hold this one: the last e with tile_start[e] <= tile
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (tile_start[mid] <= tile) lo = mid; else hi = mid;
+    }
+    const int e = lo;
+    const int m0 = offsets[e] + (tile - tile_start[e]) * MG_BM, m_end = offsets[e + 1];
+    const int n0 = blockIdx.y * MG_BN;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid < MG_BM) {
+        const int slot = m0 + tid;
+        const bool live = slot < m_end;
+        const int pair = live ? sorted[slot] : -1;
+        src_row[tid] = !live ? -1 : (UP ? pair / top : slot);
+        dst_row[tid] = !live ? -1 : (UP ? slot : pair);
+    }
+    __syncthreads();
+    const __nv_bfloat16* Wb = W + (size_t)e * N * K;
+    // staging: 64 rows x 32 columns = 256 chunks of 16 bytes per operand; a thread takes two of each
+    auto stage = [&](int buf, int k0) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int chunk = tid + i * 128, r = chunk >> 2, c = (chunk & 3) * 8;
+            const int ar = src_row[r];
+            const bool ka = k0 + c < K;
+            const int kc = ka ? k0 + c : 0;          // (an address that exists even where nothing is read)
+            mg_cp_async16(&sa[buf][r][c], A + (size_t)(ar < 0 ? 0 : ar) * lda + kc, ar >= 0 && ka);
+            const int br = n0 + r;
+            mg_cp_async16(&sb[buf][r][c], Wb + (size_t)(br < N ? br : 0) * K + kc, br < N && ka);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;       // this warp's 32 x 32 piece of the tile
+    float acc[2][4][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int t = 0; t < 4; ++t) acc[i][j][t] = 0.f;
+    const int steps = (K + MG_BK - 1) / MG_BK;
+    stage(0, 0);
+    for (int s = 0; s < steps; ++s) {
+        if (s + 1 < steps) {
+            stage((s + 1) & 1, (s + 1) * MG_BK);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const int buf = s & 1;
+#pragma unroll
+        for (int kk = 0; kk < MG_BK; kk += 16) {
+            unsigned a[2][4], b[4][2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const unsigned addr = (unsigned)__cvta_generic_to_shared(&sa[buf][wm + i * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(a[i][0]), "=r"(a[i][1]), "=r"(a[i][2]), "=r"(a[i][3]) : "r"(addr));
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {      // two 8-column tiles of W per ldmatrix.x4: rows n, columns k
+                const int nrow = wn + j * 16 + (lane & 7) + ((lane >> 4) << 3), kcol = kk + ((lane >> 3) & 1) * 8;
+                const unsigned addr = (unsigned)__cvta_generic_to_shared(&sb[buf][nrow][kcol]);
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(b[2 * j][0]), "=r"(b[2 * j][1]), "=r"(b[2 * j + 1][0]), "=r"(b[2 * j + 1][1]) : "r"(addr));
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                                 : "+f"(acc[i][j][0]), "+f"(acc[i][j][1]), "+f"(acc[i][j][2]), "+f"(acc[i][j][3])
+                                 : "r"(a[i][0]), "r"(a[i][1]), "r"(a[i][2]), "r"(a[i][3]), "r"(b[j][0]), "r"(b[j][1]));
+        }
+        __syncthreads();
+    }
+    // epilogue: thread holds rows (lane / 4) and (lane / 4 + 8) of each 16-row tile, columns 2 * (lane % 4), + 1
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = wm + i * 16 + (lane >> 2) + half * 8;
+            const int out_row = dst_row[r];
+            if (out_row < 0) continue;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int col = n0 + wn + j * 8 + (lane & 3) * 2;
+                float v0 = acc[i][j][half * 2], v1 = acc[i][j][half * 2 + 1];
+                if (UP) {
+                    v0 = fmaxf(v0, 0.f); v0 *= v0;
+                    v1 = fmaxf(v1, 0.f); v1 *= v1;
+                    __nv_bfloat16* o = (__nv_bfloat16*)C + (size_t)out_row * ldc + col;
+                    if (col + 1 < N && (ldc & 1) == 0) *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(v0, v1);
+                    else {
+                        if (col < N) o[0] = __float2bfloat16_rn(v0);
+                        if (col + 1 < N) o[1] = __float2bfloat16_rn(v1);
+                    }
+                } else {
+                    float* o = (float*)C + (size_t)out_row * ldc + col;
+                    if (col < N) o[0] = v0;
+                    if (col + 1 < N) o[1] = v1;
+                }
+            }
+        }
+}
+
+GB_EXPORT int gb_moe_sort(const int* choice, const int* positions, int n, int E, int top, int* offsets, int* tile_start, int* sorted,
+                          cudaStream_t stream) {
+    GB_REQUIRE(n >= 0 && E > 0 && E <= MOE_MAX_EXPERTS && top > 0, "gb_moe_sort: bad sizes");
+    if (n == 0) return 0;
+    gb_launch(GB_PDL_ELEMENTWISE, moe_sort_kernel, dim3(1), dim3(1024), 0, stream, choice, positions, n, E, top, offsets, tile_start, sorted);
+    return gb_check_launch("gb_moe_sort");
+}
+
+// 1 if the grouped tensor-core products take these sizes (rows of 16-byte pieces)
+GB_EXPORT int gb_moe_grouped_supported(int d, int ff) { return d % 8 == 0 && ff % 8 == 0 ? 1 : 0; }
+
+GB_EXPORT int gb_moe_grouped_gemm(const void* a, long long lda, const void* w, int N, int K, const int* sorted, const int* offsets,
+                                  const int* tile_start, int E, int top, int pairs, void* c, long long ldc, int up, cudaStream_t stream) {
+    GB_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0 && pairs >= 0, "gb_moe_grouped_gemm: rows must be whole 16-byte pieces (K=%d)", K);
+    GB_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0, "gb_moe_grouped_gemm: operands must be 16-byte aligned");
+    if (pairs == 0) return 0;
+    dim3 grid(gb_ceil_div(pairs, MG_BM) + E, gb_ceil_div(N, MG_BN));      // (at most this many tiles: blocks beyond the last return)
+    if (up)
+        gb_launch(GB_PDL_GEMM, moe_grouped_gemm_kernel<true>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)a, lda,
+                  (const __nv_bfloat16*)w, N, K, sorted, offsets, tile_start, E, top, c, ldc);
+    else
+        gb_launch(GB_PDL_GEMM, moe_grouped_gemm_kernel<false>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)a, lda,
+                  (const __nv_bfloat16*)w, N, K, sorted, offsets, tile_start, E, top, c, ldc);
+    return gb_check_launch("gb_moe_grouped_gemm");
+}

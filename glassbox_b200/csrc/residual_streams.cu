@@ -25,9 +25,35 @@ __device__ __forceinline__ float rs_block_sum(float v, float* partial) {
     return t;
 }
 
-template <typename T>
+// One column: v[s] are the streams' values (replaced by the new ones when an output is folded in); returns u.
+template <int S>
+__device__ __forceinline__ float rs_column(float (&v)[S], float yj, const float* cm, const float* cw, const float* cr, bool fold) {
+    if (fold) {
+        float nv[S];
+#pragma unroll
+        for (int t = 0; t < S; ++t) {
+            float a = 0.f;
+            {
+#pragma unroll
+                for (int s = 0; s < S; ++s)
+                    a = fmaf(cm[s * S + t], v[s], a);
+                a = fmaf(cw[t], yj, a);
+            }
+            nv[t] = a;
+        }
+#pragma unroll
+        for (int s = 0; s < S; ++s) v[s] = nv[s];
+    }
+    float u = 0.f;
+#pragma unroll
+    for (int s = 0; s < S; ++s)
+        u = fmaf(cr[s], v[s], u);
+    return u;
+}
+
+template <typename T, int S>
 __global__ void __launch_bounds__(RS_THREADS) streams_step_kernel(
-    float* __restrict__ xs, int S, int d, const float* __restrict__ y, long long ldy, const float* __restrict__ mix,
+    float* __restrict__ xs, int d, const float* __restrict__ y, long long ldy, const float* __restrict__ mix,
     const float* __restrict__ write, const float* __restrict__ read, const float* __restrict__ w, const float* __restrict__ b,
     float eps, T* __restrict__ h, float* __restrict__ u_out, const int* __restrict__ rows, const int* __restrict__ positions,
     int n_out, int n_src) {
@@ -54,40 +80,56 @@ __global__ void __launch_bounds__(RS_THREADS) streams_step_kernel(
     float* row = xs + (size_t)src * S * d;
     const bool fold = y != nullptr, keep = fold && rows == nullptr;
     float total = 0.f;
-    for (int j = threadIdx.x; j < d; j += RS_THREADS) {
-        float v[RS_MAX_STREAMS];
+    if ((d & 3) == 0 && (ldy & 3) == 0 && ((uintptr_t)xs & 15) == 0 && (y == nullptr || ((uintptr_t)y & 15) == 0) &&
+        (u_out == nullptr || ((uintptr_t)u_out & 15) == 0)) {
+        // four columns per thread and round: every load of a round (S streams and y) is asked for before the first is used
+        for (int j = threadIdx.x * 4; j < d; j += RS_THREADS * 4) {
+            float4 q[S];
 #pragma unroll
-        for (int s = 0; s < RS_MAX_STREAMS; ++s) v[s] = s < S ? row[(size_t)s * d + j] : 0.f;
-        if (fold) {
-            const float yj = y[(size_t)src * ldy + j];
-            float nv[RS_MAX_STREAMS];
+            for (int s = 0; s < S; ++s)
+                q[s] = *reinterpret_cast<const float4*>(row + (size_t)s * d + j);
+            float4 yq = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (fold) yq = *reinterpret_cast<const float4*>(y + (size_t)src * ldy + j);
+            float v[4][S];
 #pragma unroll
-            for (int t = 0; t < RS_MAX_STREAMS; ++t) {
-                float a = 0.f;
-                if (t < S) {
-#pragma unroll
-                    for (int s = 0; s < RS_MAX_STREAMS; ++s)
-                        if (s < S) a = fmaf(cm[s * S + t], v[s], a);
-                    a = fmaf(cw[t], yj, a);
-                    if (keep) row[(size_t)t * d + j] = a;
-                }
-                nv[t] = a;
+            for (int s = 0; s < S; ++s) {
+                const float4 t = q[s];
+                v[0][s] = t.x; v[1][s] = t.y; v[2][s] = t.z; v[3][s] = t.w;
             }
+            const float yv[4] = {yq.x, yq.y, yq.z, yq.w};
+            float u[4];
 #pragma unroll
-            for (int s = 0; s < RS_MAX_STREAMS; ++s) v[s] = nv[s];
+            for (int c = 0; c < 4; ++c) u[c] = rs_column<S>(v[c], yv[c], cm, cw, cr, fold);
+            if (keep) {
+#pragma unroll
+                for (int s = 0; s < S; ++s)
+                    *reinterpret_cast<float4*>(row + (size_t)s * d + j) = make_float4(v[0][s], v[1][s], v[2][s], v[3][s]);
+            }
+            *reinterpret_cast<float4*>(rs_u + j) = make_float4(u[0], u[1], u[2], u[3]);
+            total += (u[0] + u[1]) + (u[2] + u[3]);
+            if (u_out) *reinterpret_cast<float4*>(u_out + (size_t)r * d + j) = make_float4(u[0], u[1], u[2], u[3]);
         }
-        float u = 0.f;
+    } else {
+        for (int j = threadIdx.x; j < d; j += RS_THREADS) {
+            float v[S];
 #pragma unroll
-        for (int s = 0; s < RS_MAX_STREAMS; ++s)
-            if (s < S) u = fmaf(cr[s], v[s], u);
-        rs_u[j] = u;
-        total += u;
-        if (u_out) u_out[(size_t)r * d + j] = u;
+            for (int s = 0; s < S; ++s) v[s] = row[(size_t)s * d + j];
+            const float u = rs_column<S>(v, fold ? y[(size_t)src * ldy + j] : 0.f, cm, cw, cr, fold);
+            if (keep) {
+#pragma unroll
+                for (int s = 0; s < S; ++s)
+                    row[(size_t)s * d + j] = v[s];
+            }
+            rs_u[j] = u;
+            total += u;
+            if (u_out) u_out[(size_t)r * d + j] = u;
+        }
     }
+    __syncthreads();          // (the norm's second pass reads columns that other threads wrote, in the four-column form)
     if (h == nullptr) return;
     const float mean = rs_block_sum(total, partial) / (float)d;
     float dev = 0.f;
-    for (int j = threadIdx.x; j < d; j += RS_THREADS) {     // (each thread reads back what it wrote itself)
+    for (int j = threadIdx.x; j < d; j += RS_THREADS) {
         const float c = rs_u[j] - mean;
         dev = fmaf(c, c, dev);
     }
@@ -121,6 +163,25 @@ GB_EXPORT int gb_streams_broadcast(const float* x, float* xs, int n, int S, int 
     return gb_check_launch("gb_streams_broadcast");
 }
 
+template <typename T, int S>
+static void rs_launch(float* xs, int d, const float* y, long long ldy, const float* mix, const float* write, const float* read,
+                      const float* w, const float* b, float eps, T* h, float* u_out, const int* rows, const int* positions, int n_out,
+                      int n_src, cudaStream_t stream) {
+    const size_t smem = (size_t)d * 4;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(streams_step_kernel<T, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    gb_launch(GB_PDL_ELEMENTWISE, streams_step_kernel<T, S>, dim3(n_out), dim3(RS_THREADS), smem, stream, xs, d, y, ldy, mix, write, read,
+              w, b, eps, h, u_out, rows, positions, n_out, n_src);
+}
+
+template <typename T>
+static void rs_dispatch(int S, float* xs, int d, const float* y, long long ldy, const float* mix, const float* write, const float* read,
+                        const float* w, const float* b, float eps, T* h, float* u_out, const int* rows, const int* positions, int n_out,
+                        int n_src, cudaStream_t stream) {
+#define RS_CASE(N) case N: rs_launch<T, N>(xs, d, y, ldy, mix, write, read, w, b, eps, h, u_out, rows, positions, n_out, n_src, stream); break;
+    switch (S) { RS_CASE(1) RS_CASE(2) RS_CASE(3) RS_CASE(4) RS_CASE(5) RS_CASE(6) RS_CASE(7) RS_CASE(8) }
+#undef RS_CASE
+}
+
 GB_EXPORT int gb_streams_step(float* xs, int S, int d, const float* y, long long ldy, const float* mix, const float* write,
                               const float* read, const float* w, const float* b, float eps, void* h, int h_dtype, float* u_out,
                               const int* rows, const int* positions, int n_out, int n_src, cudaStream_t stream) {
@@ -128,19 +189,12 @@ GB_EXPORT int gb_streams_step(float* xs, int S, int d, const float* y, long long
     GB_REQUIRE(n_out >= 0 && n_src >= 0 && d > 0 && (size_t)d * 4 <= 160 * 1024, "gb_streams_step: bad sizes (d=%d)", d);
     GB_REQUIRE(y == nullptr || (mix != nullptr && write != nullptr), "gb_streams_step: folding in an output needs mix and write");
     GB_REQUIRE(h == nullptr || w != nullptr, "gb_streams_step: a norm needs its weight");
+    GB_REQUIRE(h == nullptr || h_dtype == GB_F32 || h_dtype == GB_BF16, "gb_streams_step: unsupported output dtype %d", h_dtype);
     if (n_out == 0) return 0;
-    const size_t smem = (size_t)d * 4;
-    if (h == nullptr || h_dtype == GB_F32) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(streams_step_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        gb_launch(GB_PDL_ELEMENTWISE, streams_step_kernel<float>, dim3(n_out), dim3(RS_THREADS), smem, stream, xs, S, d, y, ldy, mix,
-                  write, read, w, b, eps, (float*)h, u_out, rows, positions, n_out, n_src);
-    } else if (h_dtype == GB_BF16) {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(streams_step_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        gb_launch(GB_PDL_ELEMENTWISE, streams_step_kernel<__nv_bfloat16>, dim3(n_out), dim3(RS_THREADS), smem, stream, xs, S, d, y, ldy,
-                  mix, write, read, w, b, eps, (__nv_bfloat16*)h, u_out, rows, positions, n_out, n_src);
-    } else {
-        GB_REQUIRE(false, "gb_streams_step: unsupported output dtype %d", h_dtype);
-    }
+    if (h == nullptr || h_dtype == GB_F32)
+        rs_dispatch<float>(S, xs, d, y, ldy, mix, write, read, w, b, eps, (float*)h, u_out, rows, positions, n_out, n_src, stream);
+    else
+        rs_dispatch<__nv_bfloat16>(S, xs, d, y, ldy, mix, write, read, w, b, eps, (__nv_bfloat16*)h, u_out, rows, positions, n_out, n_src,
+                                   stream);
     return gb_check_launch("gb_streams_step");
 }

@@ -223,3 +223,203 @@ GB_EXPORT int gb_sigmoid_attention_rows(const void* q, void* out, int dtype, con
         GB_REQUIRE(false, "gb_sigmoid_attention_rows: unsupported dtype %d", dtype);
     return gb_check_launch("gb_sigmoid_attention_rows");
 }
+
+// ----------------------------------------------------------------------------------------------
+// Prompt portions in bfloat16 on the tensor cores. A block is 64 consecutive rows of one request x one head; its 4 warps
+// own 16 rows each. The keys any of the 64 rows can see, first_position - window + 1 .. last_position, pass in tiles of 64
+// through shared memory (cp.async, two buffers, each key's row found through the block table): S = Q K^T with mma.sync
+// m16n8k16, weights sigmoid(S * scale + bias) in float32 with the window and the causal edge applied per element, rounded
+// to bfloat16 as the A operand of O += P V (float32 sums). No running maximum, no rescaling: a key's weight does not depend
+// on the other keys. Head sizes 32, 64 or 128 for keys and for values, in any combination.
+// ----------------------------------------------------------------------------------------------
+constexpr int SAT_BM = 64, SAT_BN = 64;
+
+__device__ __forceinline__ void sat_cp16(void* smem, const void* gmem, bool valid) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+
+template <int D, int V>
+__global__ void __launch_bounds__(128) sigmoid_attention_tiles_kernel(
+    const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ kcache,
+    const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_tables, int max_pages, const int* __restrict__ seq_first_row,
+    const int* __restrict__ seq_start_pos, const float* __restrict__ head_bias, int num_seqs, int tiles_per_seq, int H, int G,
+    int page_size, long long num_pages, float scale, int window, int* __restrict__ status) {
+    constexpr int LDK = D + 8, LDV = V + 8;          // rows padded by 16 bytes: ldmatrix meets no bank twice
+    extern __shared__ __align__(16) unsigned char sat_smem[];
+    __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(sat_smem);             // [64][LDK]
+    __nv_bfloat16* sk = sq + SAT_BM * LDK;                                        // [2][64][LDK]
+    __nv_bfloat16* sv = sk + 2 * SAT_BN * LDK;                                    // [2][64][LDV]
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    const int seq = blockIdx.x / tiles_per_seq, tile = blockIdx.x % tiles_per_seq, head = blockIdx.y;
+    if (seq >= num_seqs) return;
+    const int start = seq_start_pos[seq];
+    if (start < 0) return;
+    const int r0 = seq_first_row[seq], len = seq_first_row[seq + 1] - r0;
+    if (tile * SAT_BM >= len) return;
+    const int rows = min(SAT_BM, len - tile * SAT_BM);
+    const int row0 = r0 + tile * SAT_BM, p_lo = start + tile * SAT_BM, p_hi = p_lo + rows - 1;
+    if (p_hi / page_size >= max_pages) {
+        if (threadIdx.x == 0) atomicOr(status, GB_STATUS_BAD_POSITION);
+        return;
+    }
+    const int k_lo = (window > 0 && p_lo + 1 > window) ? p_lo + 1 - window : 0;
+    const int g = head / (H / G);
+    const int* table = block_tables + (size_t)seq * max_pages;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    // Q tile
+    for (int chunk = tid; chunk < SAT_BM * (D / 8); chunk += 128) {
+        const int r = chunk / (D / 8), c = (chunk % (D / 8)) * 8;
+        sat_cp16(sq + r * LDK + c, q + ((size_t)(row0 + (r < rows ? r : 0)) * H + head) * D + c, r < rows);
+    }
+    auto stage = [&](int buf, int kb) {
+        // a thread looks up the page of the keys it copies: 64 keys x (D + V) / 8 chunks over 128 threads
+        for (int chunk = tid; chunk < SAT_BN * ((D + V) / 8); chunk += 128) {
+            const int key = chunk / ((D + V) / 8), c = (chunk % ((D + V) / 8)) * 8;
+            const int kk = kb + key;
+            long long page = kk <= p_hi ? table[kk / page_size] : -1;
+            if (kk <= p_hi && (page < 0 || page >= num_pages)) {
+                atomicOr(status, GB_STATUS_BAD_SLOT);
+                page = -1;
+            }
+            const long long at = page < 0 ? 0 : (page * G + g) * page_size + kk % page_size;
+            if (c < D) sat_cp16(sk + (buf * SAT_BN + key) * LDK + c, kcache + at * D + c, page >= 0);
+            else sat_cp16(sv + (buf * SAT_BN + key) * LDV + (c - D), vcache + at * V + (c - D), page >= 0);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int n_tiles = (p_hi - k_lo) / SAT_BN + 1;
+    stage(0, k_lo);                                   // (one group holds Q and the first keys)
+    unsigned qf[D / 16][4];
+    float o[V / 8][4];
+#pragma unroll
+    for (int j = 0; j < V / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    const float bias = head_bias ? head_bias[head] : 0.f;
+    const int my_pos0 = p_lo + warp * 16 + (lane >> 2), my_pos1 = my_pos0 + 8;       // positions of this thread's two rows
+    for (int t = 0; t < n_tiles; ++t) {
+        const int kb = k_lo + t * SAT_BN, buf = t & 1;
+        if (t + 1 < n_tiles) {
+            stage(buf ^ 1, kb + SAT_BN);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        if (t == 0) {
+#pragma unroll
+            for (int kd = 0; kd < D / 16; ++kd) {
+                const unsigned addr = (unsigned)__cvta_generic_to_shared(sq + (warp * 16 + (lane & 15)) * LDK + kd * 16 + (lane >> 4) * 8);
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(qf[kd][0]), "=r"(qf[kd][1]), "=r"(qf[kd][2]), "=r"(qf[kd][3]) : "r"(addr));
+            }
+        }
+        // a warp whose rows lie wholly before this tile's first key or (with a window) wholly behind its last visible one
+        // still walks the barriers, but skips the arithmetic
+        const int w_lo = p_lo + warp * 16, w_hi = w_lo + 15;
+        const bool any = kb <= w_hi && (window <= 0 || kb + SAT_BN - 1 > w_lo - window) && warp * 16 < rows;
+        if (any) {
+            float s[SAT_BN / 8][4];
+#pragma unroll
+            for (int j = 0; j < SAT_BN / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+            const __nv_bfloat16* kt = sk + buf * SAT_BN * LDK;
+#pragma unroll
+            for (int kd = 0; kd < D / 16; ++kd) {
+#pragma unroll
+                for (int j2 = 0; j2 < SAT_BN / 16; ++j2) {
+                    unsigned b0, b1, b2, b3;
+                    const int nrow = j2 * 16 + (lane & 7) + ((lane >> 4) << 3), kcol = kd * 16 + ((lane >> 3) & 1) * 8;
+                    const unsigned addr = (unsigned)__cvta_generic_to_shared(kt + nrow * LDK + kcol);
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(addr));
+                    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                                 : "+f"(s[2 * j2][0]), "+f"(s[2 * j2][1]), "+f"(s[2 * j2][2]), "+f"(s[2 * j2][3])
+                                 : "r"(qf[kd][0]), "r"(qf[kd][1]), "r"(qf[kd][2]), "r"(qf[kd][3]), "r"(b0), "r"(b1));
+                    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                                 : "+f"(s[2 * j2 + 1][0]), "+f"(s[2 * j2 + 1][1]), "+f"(s[2 * j2 + 1][2]), "+f"(s[2 * j2 + 1][3])
+                                 : "r"(qf[kd][0]), "r"(qf[kd][1]), "r"(qf[kd][2]), "r"(qf[kd][3]), "r"(b2), "r"(b3));
+                }
+            }
+            // weights: float32 sigmoid, the causal edge and the window per element
+            unsigned pf[SAT_BN / 16][4];
+#pragma unroll
+            for (int j = 0; j < SAT_BN / 8; ++j) {
+                float p[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = kb + j * 8 + (lane & 3) * 2 + (e & 1);
+                    const int pos = e < 2 ? my_pos0 : my_pos1;
+                    const bool sees = key <= pos && (window <= 0 || pos - key < window) && pos <= p_hi;
+                    p[e] = sees ? 1.0f / (1.0f + expf(-(s[j][e] * scale + bias))) : 0.f;
+                }
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(p[0], p[1]), hi = __floats2bfloat162_rn(p[2], p[3]);
+                pf[j >> 1][(j & 1) * 2] = *reinterpret_cast<const unsigned*>(&lo);
+                pf[j >> 1][(j & 1) * 2 + 1] = *reinterpret_cast<const unsigned*>(&hi);
+            }
+            const __nv_bfloat16* vt = sv + buf * SAT_BN * LDV;
+#pragma unroll
+            for (int kk = 0; kk < SAT_BN / 16; ++kk) {
+#pragma unroll
+                for (int n2 = 0; n2 < V / 16; ++n2) {
+                    unsigned b0, b1, b2, b3;
+                    const int krow = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, ncol = n2 * 16 + (lane >> 4) * 8;
+                    const unsigned addr = (unsigned)__cvta_generic_to_shared(vt + krow * LDV + ncol);
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(addr));
+                    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                                 : "+f"(o[2 * n2][0]), "+f"(o[2 * n2][1]), "+f"(o[2 * n2][2]), "+f"(o[2 * n2][3])
+                                 : "r"(pf[kk][0]), "r"(pf[kk][1]), "r"(pf[kk][2]), "r"(pf[kk][3]), "r"(b0), "r"(b1));
+                    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                                 : "+f"(o[2 * n2 + 1][0]), "+f"(o[2 * n2 + 1][1]), "+f"(o[2 * n2 + 1][2]), "+f"(o[2 * n2 + 1][3])
+                                 : "r"(pf[kk][0]), "r"(pf[kk][1]), "r"(pf[kk][2]), "r"(pf[kk][3]), "r"(b2), "r"(b3));
+                }
+            }
+        }
+        __syncthreads();          // everyone is done with this buffer before the round after next overwrites it
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = warp * 16 + (lane >> 2) + half * 8;
+        if (r >= rows) continue;
+        __nv_bfloat16* dst = out + ((size_t)(row0 + r) * H + head) * V;
+#pragma unroll
+        for (int j = 0; j < V / 8; ++j)
+            *reinterpret_cast<__nv_bfloat162*>(dst + j * 8 + (lane & 3) * 2) = __floats2bfloat162_rn(o[j][half * 2], o[j][half * 2 + 1]);
+    }
+}
+
+GB_EXPORT int gb_sigmoid_attention_tiles_supported(int D, int V) {
+    return (D == 32 || D == 64 || D == 128) && (V == 32 || V == 64 || V == 128) ? 1 : 0;
+}
+
+template <int D, int V>
+static int sat_launch(const void* q, void* out, const void* kcache, const void* vcache, const int* block_tables, int max_pages,
+                      const int* seq_first_row, const int* seq_start_pos, const float* head_bias, int num_seqs, int tiles_per_seq, int H,
+                      int G, int page_size, long long num_pages, float scale, int window, int* status, cudaStream_t stream) {
+    const size_t smem = ((size_t)3 * SAT_BM * (D + 8) + (size_t)2 * SAT_BN * (V + 8)) * 2;
+    cudaFuncSetAttribute(sigmoid_attention_tiles_kernel<D, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    gb_launch(GB_PDL_ATTENTION, sigmoid_attention_tiles_kernel<D, V>, dim3(num_seqs * tiles_per_seq, H), dim3(128), smem, stream,
+              (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_tables,
+              max_pages, seq_first_row, seq_start_pos, head_bias, num_seqs, tiles_per_seq, H, G, page_size, num_pages, scale, window,
+              status);
+    return gb_check_launch("gb_sigmoid_attention_tiles");
+}
+
+GB_EXPORT int gb_sigmoid_attention_tiles(const void* q, void* out, const void* kcache, const void* vcache, const int* block_tables,
+                                         int max_pages, const int* seq_first_row, const int* seq_start_pos, const float* head_bias,
+                                         int num_seqs, int max_rows_per_seq, int H, int G, int D, int V, int page_size, long long num_pages,
+                                         float scale, int window, int* status, cudaStream_t stream) {
+    GB_REQUIRE(gb_sigmoid_attention_tiles_supported(D, V), "gb_sigmoid_attention_tiles: head sizes %d / %d are not built", D, V);
+    GB_REQUIRE(num_seqs >= 0 && H > 0 && G > 0 && H % G == 0 && page_size > 0 && max_pages > 0 && window >= 0 && max_rows_per_seq > 0,
+               "gb_sigmoid_attention_tiles: bad sizes");
+    if (num_seqs == 0) return 0;
+    const int tiles = gb_ceil_div(max_rows_per_seq, SAT_BM);
+#define SAT_CASE(DD, VV)                                                                                                         \
+    if (D == DD && V == VV)                                                                                                      \
+        return sat_launch<DD, VV>(q, out, kcache, vcache, block_tables, max_pages, seq_first_row, seq_start_pos, head_bias, num_seqs, \
+                                  tiles, H, G, page_size, num_pages, scale, window, status, stream);
+    SAT_CASE(32, 32) SAT_CASE(32, 64) SAT_CASE(32, 128) SAT_CASE(64, 32) SAT_CASE(64, 64) SAT_CASE(64, 128) SAT_CASE(128, 32)
+    SAT_CASE(128, 64) SAT_CASE(128, 128)
+#undef SAT_CASE
+    GB_REQUIRE(false, "gb_sigmoid_attention_tiles: head sizes %d / %d are not built", D, V);
+}

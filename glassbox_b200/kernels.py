@@ -96,9 +96,15 @@ _SIGNATURES = {
     "gb_streams_step": [_P, _I, _I, _P, _LL, _P, _P, _P, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _P],
     "gb_qk_norm_rope_write": [_P, _LL, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _LL, _I, _P, _P],
     "gb_sigmoid_attention_rows": [_P, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
-    "gb_mingru_scan": [_P, _LL, _P, _P, _P, _LL, _LL, _P, _LL, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P],
+    "gb_sigmoid_attention_tiles_supported": [_I, _I],
+    "gb_sigmoid_attention_tiles": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
+    "gb_mingru_scan": [_P, _LL, _P, _P, _P, _LL, _LL, _P, _LL, _I, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "gb_moe_route": [_P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P, _P, _P],
     "gb_moe_expert_rows": [_P, _I, _I, _P, _P, _I, _P, _P, _I, _I, _I, _P, _P],
+    "gb_moe_expert_halves": [_P, _I, _I, _P, _P, _I, _P, _P, _I, _I, _I, _P, _P, _P],
+    "gb_moe_sort": [_P, _P, _I, _I, _I, _P, _P, _P, _P],
+    "gb_moe_grouped_supported": [_I, _I],
+    "gb_moe_grouped_gemm": [_P, _LL, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _LL, _I, _P],
     "gb_moe_combine": [_P, _P, _I, _P, _LL, _P, _P, _P, _LL, _I, _I, _I, _P],
     "gb_program_op_bytes": [],
     "gb_program_max_rows": [],
@@ -1159,13 +1165,35 @@ def sigmoid_attention_rows(q: torch.Tensor, out: torch.Tensor, kcache: torch.Ten
           kcache.shape[0], float(scale), int(window) if window else 0, _ptr(status), _stream())
 
 
+def sigmoid_attention_tiles_supported(dtype: torch.dtype, dim: int, vdim: int) -> bool:
+    return dtype == torch.bfloat16 and bool(lib().gb_sigmoid_attention_tiles_supported(dim, vdim))
+
+
+def sigmoid_attention_tiles(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
+                            seq_first_row: torch.Tensor, seq_start_pos: torch.Tensor, max_rows_per_seq: int,
+                            head_bias: Optional[torch.Tensor], heads: int, kv_heads: int, dim: int, vdim: int, page_size: int,
+                            scale: float, window: Optional[int], status: torch.Tensor) -> None:
+    """``sigmoid_attention_rows`` for runs of consecutive rows (prompt portions) in bfloat16 on the tensor cores: a block
+    takes 64 rows of one request and one head; ``max_rows_per_seq`` bounds the rows a request brings (it sizes the grid)."""
+    _cuda(q, out, kcache, vcache, block_tables, seq_first_row, seq_start_pos, head_bias, status)
+    n = q.shape[0]
+    assert q.dtype == out.dtype == kcache.dtype == vcache.dtype == torch.bfloat16
+    assert q.shape == (n, heads * dim) and out.shape == (n, heads * vdim) and q.is_contiguous() and out.is_contiguous()
+    assert block_tables.is_contiguous() and seq_first_row.shape[0] == seq_start_pos.shape[0] + 1
+    assert head_bias is None or (head_bias.dtype == torch.float32 and head_bias.numel() == heads)
+    _call("gb_sigmoid_attention_tiles", _ptr(q), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_tables), block_tables.shape[1],
+          _ptr(seq_first_row), _ptr(seq_start_pos), _ptr(head_bias), seq_start_pos.shape[0], max(int(max_rows_per_seq), 1), heads,
+          kv_heads, dim, vdim, page_size, kcache.shape[0], float(scale), int(window) if window else 0, _ptr(status), _stream())
+
+
 # ------------------------------------------------------------------------------------------------ minGRU
 def mingru_scan(proj: torch.Tensor, bias_z: torch.Tensor, bias_x: torch.Tensor, state: torch.Tensor, state_off: int, out: torch.Tensor,
                 seq_first_row: torch.Tensor, seq_start_pos: torch.Tensor, seq_slots: torch.Tensor, width: int, write_state: bool,
-                status: torch.Tensor) -> None:
+                status: torch.Tensor, max_rows: int = 0) -> None:
     """S_t = (1 - z_t) S_(t-1) + z_t c_t along each request's rows, from and to ``width`` float32 numbers at ``state_off``
     of the request's slot; z = sigmoid(proj[:, :width] + bias_z), c from u = proj[:, width:2 width] + bias_x (u + 1/2 where
-    u >= 0, sigmoid(u) elsewhere), out = S_t * silu(proj[:, 2 width:3 width]). proj float32 (a column slice is allowed)."""
+    u >= 0, sigmoid(u) elsewhere), out = S_t * silu(proj[:, 2 width:3 width]). proj float32 (a column slice is allowed).
+    ``max_rows``: a bound on the rows any request brings in this step (0: unknown, the rows of the step): it sizes the blocks."""
     _cuda(proj, bias_z, bias_x, state, out, seq_first_row, seq_start_pos, seq_slots, status)
     n = proj.shape[0]
     assert proj.dtype == torch.float32 and proj.shape[1] == 3 * width and proj.stride(1) == 1
@@ -1173,7 +1201,7 @@ def mingru_scan(proj: torch.Tensor, bias_z: torch.Tensor, bias_x: torch.Tensor, 
     assert state.dim() == 2 and state.is_contiguous() and out.shape == (n, width) and out.stride(1) == 1
     _call("gb_mingru_scan", _ptr(proj), proj.stride(0), _ptr(bias_z), _ptr(bias_x), _ptr(state), state.stride(0), state_off, _ptr(out),
           out.stride(0), _dt(out), _ptr(seq_first_row), _ptr(seq_start_pos), _ptr(seq_slots), seq_start_pos.shape[0], width,
-          state.shape[0], 1 if write_state else 0, _ptr(status), _stream())
+          state.shape[0], 1 if write_state else 0, int(max_rows) if max_rows > 0 else n, _ptr(status), _stream())
 
 
 # ------------------------------------------------------------------------------------------- routed experts
@@ -1208,6 +1236,52 @@ def moe_expert_rows(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, e
     assert pair.dtype == torch.float32 and pair.shape == (n, top * d) and pair.is_contiguous()
     _call("gb_moe_expert_rows", _ptr(h), _dt(h), d, _ptr(w_up), _ptr(w_down), ff, _ptr(choice), _ptr(positions), n, experts, top,
           _ptr(pair), _stream())
+
+
+def moe_expert_halves(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, experts: int, choice: torch.Tensor,
+                       positions: torch.Tensor, act: torch.Tensor, pair: torch.Tensor) -> None:
+    """``moe_expert_rows`` as two launches of many blocks per (row, choice), for a handful of rows: act float32 [n, top * ff]
+    receives relu(W_up[e] h)^2, pair float32 [n, top * d] the experts' outputs."""
+    _cuda(h, w_up, w_down, choice, positions, act, pair)
+    n, d = h.shape
+    top = choice.shape[1]
+    ff = w_up.shape[0] // experts
+    assert h.dtype == w_up.dtype == w_down.dtype and h.is_contiguous() and w_up.is_contiguous() and w_down.is_contiguous()
+    assert w_up.shape == (experts * ff, d) and w_down.shape == (experts * d, ff) and choice.is_contiguous()
+    assert act.dtype == pair.dtype == torch.float32 and act.shape == (n, top * ff) and pair.shape == (n, top * d)
+    assert act.is_contiguous() and pair.is_contiguous()
+    _call("gb_moe_expert_halves", _ptr(h), _dt(h), d, _ptr(w_up), _ptr(w_down), ff, _ptr(choice), _ptr(positions), n, experts, top,
+          _ptr(act), _ptr(pair), _stream())
+    global launch_count
+    launch_count += 1
+
+
+def moe_grouped_supported(dtype: torch.dtype, d: int, ff: int) -> bool:
+    return dtype == torch.bfloat16 and bool(lib().gb_moe_grouped_supported(d, ff))
+
+
+def moe_experts_grouped(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, experts: int, choice: torch.Tensor,
+                        positions: torch.Tensor, tables: torch.Tensor, act: torch.Tensor, pair: torch.Tensor) -> None:
+    """The chosen experts of many rows as grouped products on the tensor cores (bfloat16): the (row, choice) pairs are
+    sorted by expert (``tables`` int32 [2 * (experts + 1) + n * top] is the sort's scratch), then one launch computes
+    act = relu(W_up[e] h)^2 for all pairs (bfloat16 [n, top * ff], in sorted order) and one pair = W_down[e] act
+    (float32 [n, top * d], in pair order)."""
+    _cuda(h, w_up, w_down, choice, positions, tables, act, pair)
+    n, d = h.shape
+    top = choice.shape[1]
+    ff = w_up.shape[0] // experts
+    P = n * top
+    assert h.dtype == w_up.dtype == w_down.dtype == act.dtype == torch.bfloat16 and pair.dtype == torch.float32
+    assert h.is_contiguous() and w_up.is_contiguous() and w_down.is_contiguous() and act.is_contiguous() and pair.is_contiguous()
+    assert w_up.shape == (experts * ff, d) and w_down.shape == (experts * d, ff) and choice.is_contiguous()
+    assert act.shape == (n, top * ff) and pair.shape == (n, top * d)
+    assert tables.dtype == torch.int32 and tables.is_contiguous() and tables.numel() >= 2 * (experts + 1) + P
+    offsets, tile_start, order = tables[:experts + 1], tables[experts + 1:2 * (experts + 1)], tables[2 * (experts + 1):]
+    _call("gb_moe_sort", _ptr(choice), _ptr(positions), n, experts, top, _ptr(offsets), _ptr(tile_start), _ptr(order), _stream())
+    _call("gb_moe_grouped_gemm", _ptr(h), d, _ptr(w_up), ff, d, _ptr(order), _ptr(offsets), _ptr(tile_start), experts, top, P,
+          _ptr(act), ff, 1, _stream())
+    _call("gb_moe_grouped_gemm", _ptr(act), ff, _ptr(w_down), d, ff, _ptr(order), _ptr(offsets), _ptr(tile_start), experts, top, P,
+          _ptr(pair), d, 0, _stream())
 
 
 def moe_combine(pair: torch.Tensor, weight: torch.Tensor, shared: Optional[torch.Tensor], gate: Optional[torch.Tensor],

@@ -50,7 +50,8 @@ class MinGru(Mixer):
         linear(ctx, h, self.params["w_in"], proj)
         gated = ctx.scratch("att", (n, w))
         kernels.mingru_scan(proj, self.params["bias_z"], self.params["bias_x"], cache.state, 0, gated, ctx.seq_first_row,
-                            ctx.seq_start_pos, ctx.seq_slots, w, writes_cache, ctx.status)
+                            ctx.seq_start_pos, ctx.seq_slots, w, writes_cache, ctx.status,
+                            max_rows=1 if ctx.decode_only else ctx.max_rows_per_seq)
         linear(ctx, gated, self.params["wo"], residual, accumulate=not getattr(ctx, "overwrite_output", False))
 
 

@@ -21,6 +21,11 @@ from .base import FeedForward, register_part
 from .linear import linear, relu2_linear
 
 
+#: up to this many rows the experts run as weight-streaming kernels per (row, choice); above it (bfloat16) as grouped
+#: tensor-core products over the pairs sorted by expert
+GROUPED_ABOVE_ROWS = 16
+
+
 class RoutedExperts(FeedForward):
     launches_through_kernels_only = True
     can_overwrite_output = True
@@ -69,7 +74,15 @@ class RoutedExperts(FeedForward):
             shared_out = ctx.scratch("moe_shared", (n, d), torch.float32)
             linear(ctx, act, p["shared_down"], shared_out)
         pair = ctx.scratch("moe_pair", (n, self.top * d), torch.float32)
-        kernels.moe_expert_rows(h, p["w_up"], p["w_down"], self.E, choice, ctx.positions, pair)
+        if n > GROUPED_ABOVE_ROWS and kernels.moe_grouped_supported(h.dtype, d, self.ff):
+            # many rows: the pairs sorted by expert, one grouped product per half on the tensor cores
+            tables = ctx.zeros_once(f"moe_tables_{self.E}_{self.top}", 2 * (self.E + 1) + ctx.max_rows * self.top, torch.int32)
+            act = ctx.scratch("moe_act", (n, self.top * self.ff))
+            kernels.moe_experts_grouped(h, p["w_up"], p["w_down"], self.E, choice, ctx.positions, tables, act, pair)
+        else:
+            # few rows (or float32): the chosen experts' matrices streamed once per (row, choice), many blocks each
+            act = ctx.scratch("moe_act32", (n, self.top * self.ff), torch.float32)
+            kernels.moe_expert_halves(h, p["w_up"], p["w_down"], self.E, choice, ctx.positions, act, pair)
         kernels.moe_combine(pair, weight, shared_out, gate, ctx.positions, residual,
                             accumulate=not getattr(ctx, "overwrite_output", False))
 

@@ -183,6 +183,94 @@ def test_sigmoid_attention_kernels(dtype, H, G, D, V, rot, window, page):
             assert np.abs(got[r] - want[r]).max() <= 0.03 * max(1.0, np.abs(want[r]).max())
 
 
+@pytest.mark.parametrize("H, G, D, V, rot, window, page", [(4, 2, 64, 64, 32, 33, 16), (2, 1, 128, 32, 64, 100, 16), (3, 3, 32, 128, 0, None, 8),
+                                                          (8, 2, 128, 128, 32, 64, 32)])
+def test_sigmoid_attention_on_the_tensor_cores(H, G, D, V, rot, window, page):
+    """Prompt portions through the tile kernel: three requests of unequal length, the second and third continuing from a
+    cache that earlier portions filled, one padding sequence; against the plain implementation over whole sequences."""
+    from glassbox_b200 import kernels
+    rng = np.random.default_rng(H * 1000 + D + V)
+    lengths, eps, scale, base, dtype = [150, 70, 3], 1e-5, D ** -0.5, 700.0, torch.bfloat16
+    qkv = [rng.standard_normal((n, (H + G) * D + G * V)) for n in lengths]
+    gq, gk, pb = 1 + 0.3 * rng.standard_normal(D), 1 + 0.3 * rng.standard_normal(D), rng.standard_normal(H) - 2.0
+    want = []
+    for r, n in enumerate(lengths):
+        m = {"heads": H, "kv_heads": G, "dim": D, "vdim": V, "scale": scale}
+        if window:
+            m["mask"] = {"size": window}
+        if rot:
+            m["rot"] = {"dims": rot, "base": base}
+        eye = np.eye(qkv[r].shape[1])
+        W = {"q": eye[:H * D], "k": eye[H * D:(H + G) * D], "v": eye[(H + G) * D:], "q.norm": gq, "k.norm": gk, "pb": pb, "o": np.eye(H * V)}
+        want.append(plain.sigmoid_attention(qkv[r], W, "", m, eps))
+    cache = _PagedRequests(lengths, G, D, V, page, dtype, seed=V)
+    inv = _f32(base ** (-2.0 * np.arange(rot // 2) / rot)) if rot else None
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    got = [np.zeros((n, H * V)) for n in lengths]
+    at = [0, 0, 0]
+    for step in ([(1, 37), None, (0, 150)], [(2, 2), (1, 33)], [(2, 1)]):
+        live = [e for e in step if e is not None]
+        rows = [(r, at[r] + i) for r, k in live for i in range(k)]
+        meta = _steps_meta([None if e is None else (at[e[0]], e[1]) for e in step], [0] * len(step))
+        x = np.zeros((meta["n"], qkv[0].shape[1]))
+        slots, row = [-1] * meta["n"], 0
+        for e in step:
+            if e is None:
+                row += 1
+                continue
+            x[row:row + e[1]] = qkv[e[0]][at[e[0]]:at[e[0]] + e[1]]
+            for i in range(e[1]):
+                p = at[e[0]] + i
+                slots[row + i] = cache.tables[e[0]][p // page] * page + p % page
+            row += e[1]
+        n = meta["n"]
+        q = torch.zeros((n, H * D), dtype=dtype, device=DEV)
+        out = torch.zeros((n, H * V), dtype=dtype, device=DEV)
+        kernels.qk_norm_rope_write(_f32(x), _f32(gq), _f32(gk), inv, meta["positions"], _i32(slots), q, cache.k, cache.v, H, G, D, V, rot,
+                                   eps, page, True, status)
+        tables = _i32([[-1] * cache.width if e is None else cache.tables[e[0]] + [-1] * (cache.width - len(cache.tables[e[0]])) for e in step])
+        kernels.sigmoid_attention_tiles(q, out, cache.k, cache.v, tables, meta["first"], meta["start"], max(e[1] for e in live),
+                                        _f32(pb), H, G, D, V, page, scale, window, status)
+        o, row = out.float().cpu().numpy(), 0
+        for e in step:
+            if e is None:
+                row += 1
+                continue
+            got[e[0]][at[e[0]]:at[e[0]] + e[1]] = o[row:row + e[1]]
+            row += e[1]
+            at[e[0]] += e[1]
+    assert int(status.item()) == 0
+    for r in range(3):
+        assert np.abs(got[r] - want[r]).max() <= 0.03 * max(1.0, np.abs(want[r]).max()), f"request {r}"
+
+
+@pytest.mark.parametrize("window, page", [(5, 16), (64, 16), (65, 16), (100, 8), (None, 16)])
+def test_which_keys_a_tile_of_rows_sees(window, page):
+    """The crafted cache of the test below through the tile kernel: one portion of 200 rows that starts at position 130 (its
+    tiles begin in the middle of a page and of a window), then the exact sums say which keys every row took."""
+    from glassbox_b200 import kernels
+    D, V, T, start, dtype = 32, 64, 330, 130, torch.bfloat16
+    cache = _PagedRequests([T], 1, D, V, page, dtype, seed=3)
+    for j in range(T):
+        pg, off = cache.tables[0][j // page], j % page
+        cache.k[pg, 0, off, 0] = 8.0
+        cache.v[pg, 0, off, j // 8] = 2.0 ** (j % 8)
+    n = T - start
+    q = torch.zeros((n, D), dtype=dtype, device=DEV); q[:, 0] = 8.0
+    out = torch.zeros((n, V), dtype=dtype, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kernels.sigmoid_attention_tiles(q, out, cache.k, cache.v, cache.table([0]), _i32([0, n]), _i32([start]), n, None, 1, 1, D, V, page,
+                                    1.0, window, status)
+    assert int(status.item()) == 0
+    got = out.float().cpu().numpy()
+    for i in range(n):
+        want = np.zeros(V)
+        for j in range(T):
+            if plain.visible(start + i, j, window):
+                want[j // 8] += 2.0 ** (j % 8)
+        np.testing.assert_array_equal(got[i], want, err_msg=f"position {start + i}, window {window}")
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("window, page", [(5, 16), (16, 16), (17, 16), (40, 8), (None, 16)])
 def test_which_keys_a_row_sees(dtype, window, page):
@@ -353,6 +441,39 @@ def test_experts_and_their_sum(dtype, E, top, ff, d, shared):
     assert np.all(got[5] == 2.0)                                             # a padding row is left alone
     kernels.moe_combine(pair, _f32(weight), None, None, _i32(positions), out, False)
     assert np.all(out.cpu().numpy()[5] == 2.0)
+
+
+@pytest.mark.parametrize("E, top, ff, d, n", [(8, 2, 64, 128, 300), (16, 4, 40, 72, 77), (3, 3, 136, 64, 129)])
+def test_grouped_experts_equal_the_row_form(E, top, ff, d, n):
+    """The pairs sorted by expert and run as grouped tensor-core products, against the plain experts; some experts get no
+    row, some more than a tile of 64, padding rows are skipped; the split row form (float32 activations) beside it."""
+    from glassbox_b200 import kernels
+    rng = np.random.default_rng(E + ff + n)
+    rnd = lambda *s: torch.tensor(rng.standard_normal(s), dtype=torch.float32).bfloat16()
+    h, up, down = rnd(n, d), rnd(E * ff, d) / np.sqrt(d), rnd(E * d, ff) / np.sqrt(ff)
+    usable = [e for e in range(E) if e != 1 or E <= top]                         # expert 1 gets no row
+    choice = np.stack([rng.permutation(usable)[:top] for _ in range(n)]).astype(np.int32)
+    positions = list(range(n)); positions[7] = -1
+    tables = torch.zeros(2 * (E + 1) + n * top, dtype=torch.int32, device=DEV)
+    act = torch.zeros((n, top * ff), dtype=torch.bfloat16, device=DEV)
+    pair = torch.full((n, top * d), 9.0, dtype=torch.float32, device=DEV)
+    kernels.moe_experts_grouped(h.to(DEV), up.to(DEV), down.to(DEV), E, _i32(choice), _i32(positions), tables, act, pair)
+    act32 = torch.zeros((n, top * ff), dtype=torch.float32, device=DEV)
+    pair2 = torch.full((n, top * d), 9.0, dtype=torch.float32, device=DEV)
+    kernels.moe_expert_halves(h.to(DEV), up.to(DEV), down.to(DEV), E, _i32(choice), _i32(positions), act32, pair2)
+    h64, up64, down64 = (t.float().numpy().astype(np.float64) for t in (h, up, down))
+    got, got2 = pair.cpu().numpy().reshape(n, top, d), pair2.cpu().numpy().reshape(n, top, d)
+    for t in range(n):
+        if t == 7:
+            assert np.all(got[t] == 9.0) and np.all(got2[t] == 9.0)
+            continue
+        for k in range(top):
+            e = choice[t, k]
+            want = plain.expert(h64[t], up64[e * ff:(e + 1) * ff], down64[e * d:(e + 1) * d])
+            np.testing.assert_allclose(got2[t, k], want, atol=2e-3 * max(1.0, np.abs(want).max()), rtol=2e-3)
+            np.testing.assert_allclose(got[t, k], want, atol=2e-2 * max(1.0, np.abs(want).max()), rtol=2e-2)
+    counts = tables[:E + 1].cpu().numpy()
+    assert counts[E] == (n - 1) * top and (E <= top or counts[2] == counts[1])   # every live pair sorted; expert 1 empty
 
 
 # ------------------------------------------------------------------------------------------- whole models
