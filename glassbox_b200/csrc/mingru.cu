@@ -12,18 +12,19 @@
 // the piece borders; a portion of one row (decoding) is the plain update.
 #include "common.cuh"
 
-constexpr int MG_CH = 32;          // channels per block: a warp's lanes
-constexpr int MG_PARTS = 32;       // at most this many pieces of the rows: the block's warps (the launch says how many)
+constexpr int MG_CH = 32;          // channels per block: a warp's lanes (16 for long portions: twice the pieces per block)
+constexpr int MG_PARTS = 64;       // at most this many pieces of the rows (the launch says how many: blockDim.x / channels)
 constexpr int MG_MIN_PIECE = 8;    // shorter portions are walked by fewer groups
+constexpr int MG_THREADS = 1024;
 
 __device__ __forceinline__ float mg_sigmoid(float v) { return 1.0f / (1.0f + expf(-v)); }
 
 template <typename T>
-__global__ void __launch_bounds__(MG_CH * MG_PARTS) mingru_scan_kernel(     // (blockDim.x / 32 warps = the most pieces)
+__global__ void __launch_bounds__(MG_THREADS) mingru_scan_kernel(
     const float* __restrict__ proj, long long ld, const float* __restrict__ bz, const float* __restrict__ bx,
     float* __restrict__ state, long long state_stride, long long state_off, T* __restrict__ out, long long ldo,
     const int* __restrict__ seq_first_row, const int* __restrict__ seq_start_pos, const int* __restrict__ seq_slots, int S, int width,
-    int num_slots, int write_state, int* __restrict__ status) {
+    int num_slots, int write_state, int chw, int* __restrict__ status) {
     __shared__ float sa[MG_PARTS][MG_CH], sb[MG_PARTS][MG_CH];
     gb_pdl_launch_dependents();
     gb_pdl_wait();
@@ -34,12 +35,12 @@ __global__ void __launch_bounds__(MG_CH * MG_PARTS) mingru_scan_kernel(     // (
         if (threadIdx.x == 0) atomicOr(status, GB_STATUS_BAD_SLOT);
         return;
     }
-    const int lane = threadIdx.x & 31, part = threadIdx.x >> 5;
-    const int ch = blockIdx.y * MG_CH + lane;
+    const int lane = threadIdx.x % chw, part = threadIdx.x / chw;      // chw channels per block, blockDim.x / chw pieces
+    const int ch = blockIdx.y * chw + lane;
     const bool live = ch < width;
     const int r0 = seq_first_row[seq], len = seq_first_row[seq + 1] - r0;
     int parts = (len + MG_MIN_PIECE - 1) / MG_MIN_PIECE;
-    const int most = (int)(blockDim.x >> 5);
+    const int most = (int)blockDim.x / chw;
     parts = parts < 1 ? 1 : (parts > most ? most : parts);
     const int piece = (len + parts - 1) / parts;
     const int lo = r0 + part * piece, hi = min(lo + piece, r0 + len);
@@ -89,19 +90,21 @@ GB_EXPORT int gb_mingru_scan(const float* proj, long long ld, const float* bz, c
     GB_REQUIRE(S >= 0 && width > 0 && num_slots > 0, "gb_mingru_scan: bad sizes");
     GB_REQUIRE(state_off >= 0 && state_off + width <= state_stride, "gb_mingru_scan: the state does not fit its slot");
     if (S == 0) return 0;
-    dim3 grid(S, gb_ceil_div(width, MG_CH));
-    // as many warps as the longest portion of the step has pieces (the caller's bound on a request's rows in this step)
-    int warps = gb_ceil_div(max_rows > 0 ? max_rows : 1, MG_MIN_PIECE);
-    warps = warps < 1 ? 1 : (warps > MG_PARTS ? MG_PARTS : warps);
-    const dim3 block(MG_CH * warps);
+    // as many pieces as the longest portion of the step has (the caller's bound on a request's rows in this step); long
+    // portions take 16 channels per block, so that a block of 1024 threads cuts them into 64 pieces
+    int pieces = gb_ceil_div(max_rows > 0 ? max_rows : 1, MG_MIN_PIECE);
+    const int chw = pieces > MG_THREADS / MG_CH ? 16 : MG_CH;
+    pieces = pieces < 1 ? 1 : (pieces > MG_THREADS / chw ? MG_THREADS / chw : pieces);
+    dim3 grid(S, gb_ceil_div(width, chw));
+    const dim3 block(((chw * pieces + 31) / 32) * 32);
     if (out_dtype == GB_F32)
         gb_launch(GB_PDL_ELEMENTWISE, mingru_scan_kernel<float>, grid, block, 0, stream, proj, ld, bz, bx, state,
                   state_stride, state_off, (float*)out, ldo, seq_first_row, seq_start_pos, seq_slots, S, width, num_slots, write_state,
-                  status);
+                  chw, status);
     else if (out_dtype == GB_BF16)
         gb_launch(GB_PDL_ELEMENTWISE, mingru_scan_kernel<__nv_bfloat16>, grid, block, 0, stream, proj, ld, bz, bx, state,
                   state_stride, state_off, (__nv_bfloat16*)out, ldo, seq_first_row, seq_start_pos, seq_slots, S, width, num_slots,
-                  write_state, status);
+                  write_state, chw, status);
     else
         GB_REQUIRE(false, "gb_mingru_scan: unsupported output dtype %d", out_dtype);
     return gb_check_launch("gb_mingru_scan");

@@ -27,6 +27,7 @@ template <>
 __device__ __forceinline__ float moe_warp_dot<float>(const float* __restrict__ w, const float* __restrict__ x, int K, int lane) {
     float d = 0.f;
     if (K % 4 == 0 && ((uintptr_t)w & 15) == 0) {
+#pragma unroll 4
         for (int i = lane * 4; i < K; i += 128) {
             const float4 v = *reinterpret_cast<const float4*>(w + i);
             d = fmaf(v.x, x[i], d); d = fmaf(v.y, x[i + 1], d); d = fmaf(v.z, x[i + 2], d); d = fmaf(v.w, x[i + 3], d);
@@ -42,6 +43,7 @@ __device__ __forceinline__ float moe_warp_dot<__nv_bfloat16>(const __nv_bfloat16
                                                              int lane) {
     float d = 0.f;
     if (K % 8 == 0 && ((uintptr_t)w & 15) == 0) {
+#pragma unroll 4
         for (int i = lane * 8; i < K; i += 256) {
             const uint4 raw = *reinterpret_cast<const uint4*>(w + i);
             const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);

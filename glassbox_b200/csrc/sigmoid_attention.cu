@@ -15,7 +15,7 @@ constexpr int SA_MAX_DIM = 256;
 constexpr int SA_WARPS = 4;
 
 template <typename T>
-__global__ void __launch_bounds__(128) qk_norm_rope_write_kernel(
+__global__ void __launch_bounds__(512) qk_norm_rope_write_kernel(
     const float* __restrict__ qkv, long long ld, const float* __restrict__ q_gain, const float* __restrict__ k_gain,
     const float* __restrict__ inv_freq, const int* __restrict__ positions, const int* __restrict__ slots, T* __restrict__ q_out,
     T* __restrict__ kcache, T* __restrict__ vcache, int n, int H, int G, int D, int V, int rot, float eps, int page_size,
@@ -86,12 +86,13 @@ GB_EXPORT int gb_qk_norm_rope_write(const float* qkv, long long ld, const float*
     GB_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= D, "gb_qk_norm_rope_write: %d rotated channels of %d", rot, D);
     GB_REQUIRE(rot == 0 || inv_freq != nullptr, "gb_qk_norm_rope_write: a rotation needs its frequencies");
     if (n == 0) return 0;
+    const dim3 block(32 * (H + G < 4 ? 4 : (H + G > 16 ? 16 : H + G)));      // a warp per head, up to 16 at a time
     if (dtype == GB_F32)
-        gb_launch(GB_PDL_ELEMENTWISE, qk_norm_rope_write_kernel<float>, dim3(n), dim3(128), 0, stream, qkv, ld, q_gain, k_gain, inv_freq,
+        gb_launch(GB_PDL_ELEMENTWISE, qk_norm_rope_write_kernel<float>, dim3(n), block, 0, stream, qkv, ld, q_gain, k_gain, inv_freq,
                   positions, slots, (float*)q_out, (float*)kcache, (float*)vcache, n, H, G, D, V, rot, eps, page_size, num_slots,
                   write_kv, status);
     else if (dtype == GB_BF16)
-        gb_launch(GB_PDL_ELEMENTWISE, qk_norm_rope_write_kernel<__nv_bfloat16>, dim3(n), dim3(128), 0, stream, qkv, ld, q_gain, k_gain,
+        gb_launch(GB_PDL_ELEMENTWISE, qk_norm_rope_write_kernel<__nv_bfloat16>, dim3(n), block, 0, stream, qkv, ld, q_gain, k_gain,
                   inv_freq, positions, slots, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, n, H, G, D, V,
                   rot, eps, page_size, num_slots, write_kv, status);
     else
@@ -107,6 +108,7 @@ template <>
 __device__ __forceinline__ float sa_dot<float>(const float* __restrict__ q, const float* __restrict__ k, int D) {
     float d = 0.f;
     if (D % 4 == 0 && ((uintptr_t)k & 15) == 0) {
+#pragma unroll 8
         for (int i = 0; i < D; i += 4) {
             const float4 kv = *reinterpret_cast<const float4*>(k + i);
             d = fmaf(q[i], kv.x, d); d = fmaf(q[i + 1], kv.y, d); d = fmaf(q[i + 2], kv.z, d); d = fmaf(q[i + 3], kv.w, d);
@@ -121,6 +123,7 @@ template <>
 __device__ __forceinline__ float sa_dot<__nv_bfloat16>(const float* __restrict__ q, const __nv_bfloat16* __restrict__ k, int D) {
     float d = 0.f;
     if (D % 8 == 0 && ((uintptr_t)k & 15) == 0) {
+#pragma unroll 8
         for (int i = 0; i < D; i += 8) {
             const uint4 raw = *reinterpret_cast<const uint4*>(k + i);
             const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -222,6 +225,126 @@ GB_EXPORT int gb_sigmoid_attention_rows(const void* q, void* out, int dtype, con
     else
         GB_REQUIRE(false, "gb_sigmoid_attention_rows: unsupported dtype %d", dtype);
     return gb_check_launch("gb_sigmoid_attention_rows");
+}
+
+// ----------------------------------------------------------------------------------------------
+// Single decoded tokens: one block of 8 warps per (row, head). The warps take the row's visible keys 32 at a time in turn
+// (warp w the chunks w, w + 8, ...): a lane per key for the score, then a lane per pair of value channels for the sum, four
+// keys' loads in flight at once; the warps' partial sums meet in shared memory and are added in a fixed order. The order
+// of a row's sums depends on its position and the window alone. Value sizes must be even.
+// ----------------------------------------------------------------------------------------------
+constexpr int SAD_WARPS = 8;
+
+__device__ __forceinline__ float2 sad_load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 sad_load2(const __nv_bfloat16* p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(SAD_WARPS * 32) sigmoid_attention_decode_kernel(
+    const T* __restrict__ q, T* __restrict__ out, const T* __restrict__ kcache, const T* __restrict__ vcache,
+    const int* __restrict__ block_tables, int max_pages, const int* __restrict__ row_seq, const int* __restrict__ positions,
+    const float* __restrict__ head_bias, int n, int H, int G, int D, int V, int page_size, long long num_pages, float scale,
+    int window, int* __restrict__ status) {
+    __shared__ __align__(16) float qs[SA_MAX_DIM];
+    __shared__ float part[SAD_WARPS][SA_MAX_DIM];
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    const int row = blockIdx.x, head = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (row >= n) return;
+    const int pos = positions[row];
+    if (pos < 0) return;
+    if (pos / page_size >= max_pages) {
+        if (threadIdx.x == 0) atomicOr(status, GB_STATUS_BAD_POSITION);
+        return;
+    }
+    const int g = head / (H / G);
+    const int* table = block_tables + (size_t)row_seq[row] * max_pages;
+    const T* qrow = q + ((size_t)row * H + head) * D;
+    for (int i = threadIdx.x; i < D; i += SAD_WARPS * 32) qs[i] = gb_to_float(qrow[i]);
+    __syncthreads();
+    const float bias = head_bias ? head_bias[head] : 0.f;
+    const int first = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+    const int chunks = (pos - first) / 32 + 1;
+    constexpr int NJ = SA_MAX_DIM / 64;
+    float2 acc[NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) acc[j] = make_float2(0.f, 0.f);
+    for (int c = warp; c < chunks; c += SAD_WARPS) {
+        const int key = first + c * 32 + lane;
+        float p = 0.f;
+        long long at = -1;
+        if (key <= pos) {
+            const long long page = table[key / page_size];
+            if (page < 0 || page >= num_pages) {
+                atomicOr(status, GB_STATUS_BAD_SLOT);
+            } else {
+                at = (page * G + g) * page_size + key % page_size;
+                const float sc = sa_dot<T>(qs, kcache + at * D, D) * scale + bias;
+                p = 1.0f / (1.0f + expf(-sc));
+            }
+        }
+#pragma unroll 2
+        for (int t0 = 0; t0 < 32; t0 += 4) {
+            float pt[4];
+            float2 val[4][NJ];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                pt[u] = __shfl_sync(0xffffffffu, p, t0 + u);
+                const long long vr = __shfl_sync(0xffffffffu, at, t0 + u);
+#pragma unroll
+                for (int j = 0; j < NJ; ++j) {
+                    const int i = 2 * lane + 64 * j;
+                    val[u][j] = (vr >= 0 && i < V) ? sad_load2(vcache + vr * V + i) : make_float2(0.f, 0.f);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int j = 0; j < NJ; ++j) {
+                    acc[j].x = fmaf(pt[u], val[u][j].x, acc[j].x);
+                    acc[j].y = fmaf(pt[u], val[u][j].y, acc[j].y);
+                }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+        const int i = 2 * lane + 64 * j;
+        if (i < V) {
+            part[warp][i] = acc[j].x;
+            part[warp][i + 1] = acc[j].y;
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < V; i += SAD_WARPS * 32) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < SAD_WARPS; ++w) t += part[w][i];
+        out[((size_t)row * H + head) * V + i] = gb_from_float<T>(t);
+    }
+}
+
+GB_EXPORT int gb_sigmoid_attention_decode(const void* q, void* out, int dtype, const void* kcache, const void* vcache,
+                                          const int* block_tables, int max_pages, const int* row_seq, const int* positions,
+                                          const float* head_bias, int n, int H, int G, int D, int V, int page_size, long long num_pages,
+                                          float scale, int window, int* status, cudaStream_t stream) {
+    GB_REQUIRE(n >= 0 && H > 0 && G > 0 && H % G == 0, "gb_sigmoid_attention_decode: heads %d must be a multiple of kv heads %d", H, G);
+    GB_REQUIRE(D > 0 && D <= SA_MAX_DIM && V > 0 && V <= SA_MAX_DIM && V % 2 == 0,
+               "gb_sigmoid_attention_decode: head sizes %d / %d (values: even) are outside 1..%d", D, V, SA_MAX_DIM);
+    GB_REQUIRE(page_size > 0 && max_pages > 0 && window >= 0, "gb_sigmoid_attention_decode: bad page geometry or window");
+    if (n == 0) return 0;
+    if (dtype == GB_F32)
+        gb_launch(GB_PDL_ATTENTION, sigmoid_attention_decode_kernel<float>, dim3(n, H), dim3(SAD_WARPS * 32), 0, stream, (const float*)q,
+                  (float*)out, (const float*)kcache, (const float*)vcache, block_tables, max_pages, row_seq, positions, head_bias, n, H,
+                  G, D, V, page_size, num_pages, scale, window, status);
+    else if (dtype == GB_BF16)
+        gb_launch(GB_PDL_ATTENTION, sigmoid_attention_decode_kernel<__nv_bfloat16>, dim3(n, H), dim3(SAD_WARPS * 32), 0, stream,
+                  (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_tables,
+                  max_pages, row_seq, positions, head_bias, n, H, G, D, V, page_size, num_pages, scale, window, status);
+    else
+        GB_REQUIRE(false, "gb_sigmoid_attention_decode: unsupported dtype %d", dtype);
+    return gb_check_launch("gb_sigmoid_attention_decode");
 }
 
 // ----------------------------------------------------------------------------------------------
@@ -351,7 +474,7 @@ __global__ void __launch_bounds__(128) sigmoid_attention_tiles_kernel(
                     const int key = kb + j * 8 + (lane & 3) * 2 + (e & 1);
                     const int pos = e < 2 ? my_pos0 : my_pos1;
                     const bool sees = key <= pos && (window <= 0 || pos - key < window) && pos <= p_hi;
-                    p[e] = sees ? 1.0f / (1.0f + expf(-(s[j][e] * scale + bias))) : 0.f;
+                    p[e] = sees ? __fdividef(1.0f, 1.0f + __expf(-(s[j][e] * scale + bias))) : 0.f;      // (rounded to bfloat16 next)
                 }
                 const __nv_bfloat162 lo = __floats2bfloat162_rn(p[0], p[1]), hi = __floats2bfloat162_rn(p[2], p[3]);
                 pf[j >> 1][(j & 1) * 2] = *reinterpret_cast<const unsigned*>(&lo);

@@ -74,8 +74,14 @@ class SigmoidAttention(Mixer):
         linear(ctx, att, self.params["wo"], residual, accumulate=not getattr(ctx, "overwrite_output", False))
 
     def attend(self, ctx, q, att, cache) -> None:
-        """Prompt portions in bfloat16 at head sizes the tile kernel is built for run on the tensor cores; single decoded
-        tokens, float32 and other sizes take the one-warp-per-(row, head) kernel."""
+        """Single decoded tokens take the kernel that shares a row's keys between the warps of a block; prompt portions in
+        bfloat16 at head sizes the tile kernel is built for run on the tensor cores; everything else (float32 portions,
+        other sizes) takes the one-warp-per-(row, head) kernel."""
+        if ctx.decode_only and self.V % 2 == 0:
+            kernels.sigmoid_attention_decode(q, att, cache.k, cache.v, cache.block_tables, ctx.row_seq, ctx.positions,
+                                             self.params.get("head_bias"), self.H, self.G, self.D, self.V, cache.page_size,
+                                             self.spec.scale, self.spec.window, ctx.status)
+            return
         if not ctx.decode_only and kernels.sigmoid_attention_tiles_supported(q.dtype, self.D, self.V):
             kernels.sigmoid_attention_tiles(q, att, cache.k, cache.v, cache.block_tables, ctx.seq_first_row, ctx.seq_start_pos,
                                             ctx.max_rows_per_seq, self.params.get("head_bias"), self.H, self.G, self.D, self.V,

@@ -167,8 +167,10 @@ def test_sigmoid_attention_kernels(dtype, H, G, D, V, rot, window, page):
         positions, row_seq = _i32([p for _, p in rows]), _i32([i for i, (r, k) in enumerate(step) for _ in range(k)])
         kernels.qk_norm_rope_write(x, _f32(gq), _f32(gk), inv, positions, cache.slots(rows), q, cache.k, cache.v, H, G, D, V, rot, eps,
                                    page, True, status)
-        kernels.sigmoid_attention_rows(q, out, cache.k, cache.v, cache.table([r for r, _ in step]), row_seq, positions, _f32(pb), H,
-                                       G, D, V, page, scale, window, status)
+        single = all(k == 1 for _, k in step) and V % 2 == 0          # single tokens: the kernel that decoding uses
+        attend = kernels.sigmoid_attention_decode if single else kernels.sigmoid_attention_rows
+        attend(q, out, cache.k, cache.v, cache.table([r for r, _ in step]), row_seq, positions, _f32(pb), H, G, D, V, page, scale, window,
+               status)
         o = out.float().cpu().numpy()
         i = 0
         for r, k in step:
@@ -292,20 +294,22 @@ def test_which_keys_a_row_sees(dtype, window, page):
     q = torch.zeros((len(rows), D), dtype=dtype, device=DEV); q[:, 0] = 8.0
     out = torch.zeros((len(rows), V), dtype=dtype, device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    kernels.sigmoid_attention_rows(q, out, cache.k, cache.v, cache.table([0]), _i32([0] * len(rows)), _i32(rows), None, 1, 1, D, V, page,
-                                   1.0, window, status)
-    assert int(status.item()) == 0
-    got = out.float().cpu().numpy()
-    for i, p in enumerate(rows):
-        want = np.zeros(V)
-        for j in range(T):
-            if plain.visible(p, j, window):
-                want[j // 8] += 2.0 ** (j % 8)
-        np.testing.assert_array_equal(got[i], want, err_msg=f"position {p}, window {window}")
+    for attend in (kernels.sigmoid_attention_rows, kernels.sigmoid_attention_decode):
+        out.zero_()
+        attend(q, out, cache.k, cache.v, cache.table([0]), _i32([0] * len(rows)), _i32(rows), None, 1, 1, D, V, page, 1.0, window, status)
+        assert int(status.item()) == 0
+        got = out.float().cpu().numpy()
+        for i, p in enumerate(rows):
+            want = np.zeros(V)
+            for j in range(T):
+                if plain.visible(p, j, window):
+                    want[j // 8] += 2.0 ** (j % 8)
+            np.testing.assert_array_equal(got[i], want, err_msg=f"{attend.__name__}: position {p}, window {window}")
 
 
 @pytest.mark.parametrize("width", [1, 13, 72, 256])
-def test_mingru_scan_carries_its_state(width):
+@pytest.mark.parametrize("bound", [0, 600])
+def test_mingru_scan_carries_its_state(width, bound):
     """Portions of 1, 2, a few and many rows (the kernel cuts long ones into pieces), requests side by side with a padding
     sequence between them, slots of other requests untouched."""
     from glassbox_b200 import kernels
@@ -334,7 +338,8 @@ def test_mingru_scan_carries_its_state(width):
             x[row:row + e[1]] = proj[e[0]][at[e[0]]:at[e[0]] + e[1]]
             row += e[1]
         out = torch.zeros((meta["n"], width), dtype=torch.float32, device=DEV)
-        kernels.mingru_scan(_f32(x), _f32(bz), _f32(bx), state, 1, out, meta["first"], meta["start"], meta["slots"], width, True, status)
+        kernels.mingru_scan(_f32(x), _f32(bz), _f32(bx), state, 1, out, meta["first"], meta["start"], meta["slots"], width, True, status,
+                            max_rows=bound)          # (600: the form for long portions, 16 channels and 64 pieces per block)
         o, row = out.cpu().numpy(), 0
         for e in step:
             if e is None:
