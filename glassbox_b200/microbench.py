@@ -14,6 +14,11 @@ over operands that rotate through more memory than L2 holds.
     python -m glassbox_b200.microbench latent_attention                  attention over a latent cache (prompt and decoding) beside
                                                                          grouped-query attention of like size
     python -m glassbox_b200.microbench delta_rule                        the delta-rule recurrence over a prompt and for single tokens
+    python -m glassbox_b200.microbench lonorax                           Lonorax's kernels, each beside its like kernel: sigmoid attention
+                                                                         (window 1024) beside grouped-query attention with the same
+                                                                         window; the grouped experts' products beside a dense product of
+                                                                         as many multiply-adds; minGRU beside the delta rule; the streams'
+                                                                         row kernel beside RMSNorm
 
 Prints one line per case: microseconds and GB/s or TFLOP/s of the algorithmic bytes or flops. With ``--once`` after
 the case's name every kernel is launched exactly once and nothing is timed: the form in which a profiler captures one
@@ -263,6 +268,130 @@ def bench_delta_rule() -> None:
     kernels.check_status(status)
 
 
+def bench_lonorax() -> None:
+    """Each kernel of the Lonorax path beside the like kernel of the other paths, at the sizes of the width-1024 and
+    width-2048 models that ``bench.py --workload lonorax`` runs."""
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ps, hd, window, t_len = 16, 64, 1024, 2048
+    for H, G in ((16, 4), (32, 8)):
+        per = t_len // ps
+        kc = torch.randn(per + 2, G, ps, hd, device=DEV).bfloat16()
+        vc = torch.randn_like(kc)
+        tables = torch.arange(per, dtype=torch.int32, device=DEV).view(1, per).contiguous()
+        first = torch.tensor([0, t_len], dtype=torch.int32, device=DEV)
+        start = torch.zeros(1, dtype=torch.int32, device=DEV)
+        q = torch.randn(t_len, H * hd, device=DEV).bfloat16()
+        o = torch.empty_like(q)
+        bias = torch.full((H,), -2.0, device=DEV)
+        # multiply-adds over the keys a row sees: rows below the window see all earlier keys, the others `window`
+        seen = sum(min(p + 1, window) for p in range(t_len))
+        fl = 2.0 * seen * H * (hd + hd)
+        t = graph_time(lambda: kernels.sigmoid_attention_tiles(q, o, kc, vc, tables, first, start, t_len, bias, H, G, hd, hd, ps,
+                                                               hd ** -0.5, window, status), reps=6)
+        print(f"sigmoid_attention prompt heads {H}/{G} x {hd}, window {window}, {t_len} tokens: {t:7.1f} us {fl / t / 1e6:6.1f} TFLOP/s", flush=True)
+        for name, fn in (("mma.sync", kernels.attention_prefill), ("tcgen05", kernels.attention_prefill_tc)):
+            t = graph_time(lambda: fn(q, o, kc, vc, tables, first, start, t_len, H, G, hd, ps, hd ** -0.5, window, status), reps=6)
+            print(f"   grouped-query prompt ({name}) the same heads and window: {t:7.1f} us {fl / t / 1e6:6.1f} TFLOP/s", flush=True)
+        ctx = 4096
+        for m in (1, 8, 64):
+            per = ctx // ps
+            kc = torch.randn(m * per + 4, G, ps, hd, device=DEV).bfloat16()
+            vc = torch.randn_like(kc)
+            tables = torch.arange(m * per, dtype=torch.int32, device=DEV).view(m, per).contiguous()
+            row_seq = torch.arange(m, dtype=torch.int32, device=DEV)
+            pos = torch.full((m,), ctx - 1, dtype=torch.int32, device=DEV)
+            q = torch.randn(m, H * hd, device=DEV).bfloat16()
+            o = torch.empty_like(q)
+            nbytes = m * window * G * hd * 2 * 2
+            t = graph_time(lambda: kernels.sigmoid_attention_decode(q, o, kc, vc, tables, row_seq, pos, bias, H, G, hd, hd, ps, hd ** -0.5,
+                                                                    window, status))
+            print(f"sigmoid_attention decode heads {H}/{G} x {hd} batch {m:3d} window {window}: {t:7.1f} us {nbytes / t / 1e3:6.0f} GB/s", flush=True)
+            sp, block_keys, warps = kernels.decode_mma_plan(m, G, hd, window)
+            pa = torch.empty(m * H * warps * sp * hd, device=DEV)
+            pm = torch.empty(m * H * warps * sp * 2, device=DEV)
+            cn = torch.zeros(m * G, dtype=torch.int32, device=DEV)
+            t = graph_time(lambda: kernels.attention_decode_mma(q, o, kc, vc, tables, row_seq, pos, H, G, hd, ps, hd ** -0.5, window,
+                                                                sp, pa, pm, cn, status, block_keys, warps))
+            print(f"   grouped-query decode the same heads and window: {t:7.1f} us {nbytes / t / 1e3:6.0f} GB/s", flush=True)
+    # the routed experts: 16 experts, two per token, beside the dense product of as many multiply-adds (the shared expert's)
+    for d, ff in ((1024, 1024), (2048, 2048)):
+        E, top = 16, 2
+        for n in (2048, 64, 8):
+            h = (torch.randn(n, d, device=DEV) * 0.5).bfloat16()
+            ups = [(torch.randn(E * ff, d, device=DEV) * 0.03).bfloat16() for _ in range(3)]
+            downs = [(torch.randn(E * d, ff, device=DEV) * 0.03).bfloat16() for _ in range(3)]
+            choice = torch.stack([torch.randperm(E, device=DEV)[:top] for _ in range(n)]).int().contiguous()
+            positions = torch.arange(n, dtype=torch.int32, device=DEV)
+            pair = torch.empty(n, top * d, device=DEV)
+            turn = [0]
+            fl = 2.0 * n * top * 2 * d * ff
+            if n > 16:
+                tabs = torch.zeros(2 * (E + 1) + n * top, dtype=torch.int32, device=DEV)
+                act = torch.empty(n, top * ff, device=DEV).bfloat16()
+
+                def fn():
+                    turn[0] += 1
+                    kernels.moe_experts_grouped(h, ups[turn[0] % 3], downs[turn[0] % 3], E, choice, positions, tabs, act, pair)
+            else:
+                act = torch.empty(n, top * ff, device=DEV)
+
+                def fn():
+                    turn[0] += 1
+                    kernels.moe_expert_halves(h, ups[turn[0] % 3], downs[turn[0] % 3], E, choice, positions, act, pair)
+            t = graph_time(fn, reps=6)
+            used = min(E, n * top) * 2 * d * ff * 2          # bytes of the experts that any row chose (at most all)
+            print(f"routed experts {E} x ({d} -> {ff} -> {d}), {top} per token, {n:4d} rows: {t:7.1f} us {fl / t / 1e6:6.1f} TFLOP/s "
+                  f"{used / t / 1e3:6.0f} GB/s of chosen weights", flush=True)
+            w1 = _rotating(2 * ff, d)
+            w2 = _rotating(d, 2 * ff)
+            a1 = torch.empty(n, 2 * ff, device=DEV).bfloat16()
+            out = torch.empty(n, d, device=DEV)
+
+            def dense():
+                turn[0] += 1
+                if n > 64:
+                    kernels.gemm_tc(h, w1[turn[0] % len(w1)], a1, False, status, relu2=True)
+                    kernels.gemm_tc(a1, w2[turn[0] % len(w2)], out, False, status)
+                else:
+                    kernels.gemm_stream(h, w1[turn[0] % len(w1)], a1, relu2=True)
+                    kernels.gemm_stream(a1, w2[turn[0] % len(w2)], out)
+            t = graph_time(dense, reps=6)
+            print(f"   dense squared-ReLU feed-forward {d} -> {2 * ff} -> {d} (as many multiply-adds), {n:4d} rows: {t:7.1f} us "
+                  f"{fl / t / 1e6:6.1f} TFLOP/s {2 * 2 * d * ff * 2 / t / 1e3:6.0f} GB/s", flush=True)
+    # minGRU: the scan over a prompt (reads the float32 projections twice, writes the gated output) and for single tokens
+    for width in (2048, 4096):
+        for n, S in ((2048, 1), (64, 64)):
+            proj = torch.randn(n, 3 * width, device=DEV)
+            bz, bx = torch.randn(width, device=DEV), torch.randn(width, device=DEV)
+            state = torch.zeros(S, width, device=DEV)
+            out = torch.empty(n, width, device=DEV).bfloat16()
+            per = n // S
+            first = torch.arange(0, n + 1, per, dtype=torch.int32, device=DEV)
+            start = torch.zeros(S, dtype=torch.int32, device=DEV)
+            slots = torch.arange(S, dtype=torch.int32, device=DEV)
+            t = graph_time(lambda: kernels.mingru_scan(proj, bz, bx, state, 0, out, first, start, slots, width, True, status, max_rows=per),
+                           reps=6)
+            nbytes = n * width * (3 * 4 + 2)
+            print(f"mingru width {width}, {S} requests x {per} rows: {t:7.1f} us {nbytes / t / 1e3:6.0f} GB/s (projections once + output)", flush=True)
+    # the streams' row kernel (fold + read + layer norm over four streams) beside RMSNorm over one row
+    for d in (1024, 2048):
+        for n in (2048, 8):
+            S = 4
+            xs = torch.randn(n, S * d, device=DEV)
+            y = torch.randn(n, d, device=DEV)
+            mix, write, read = torch.eye(S, device=DEV).contiguous(), torch.ones(S, device=DEV), torch.full((S,), 0.25, device=DEV)
+            w, b = torch.ones(d, device=DEV), torch.zeros(d, device=DEV)
+            h = torch.empty(n, d, device=DEV).bfloat16()
+            positions = torch.arange(n, dtype=torch.int32, device=DEV)
+            t = graph_time(lambda: kernels.streams_step(xs, S, fold=(y, mix, write), read=read, norm=(w, b, 1e-6), h=h, positions=positions))
+            nbytes = n * d * (2 * S * 4 + 4 + 2)
+            print(f"streams fold + read + layer norm, {S} streams x {d}, {n:4d} rows: {t:7.1f} us {nbytes / t / 1e3:6.0f} GB/s", flush=True)
+            x = torch.randn(n, d, device=DEV)
+            t = graph_time(lambda: kernels.rmsnorm(x, w, h, 1e-6))
+            print(f"   RMSNorm {d}, {n:4d} rows: {t:7.1f} us {n * d * 6 / t / 1e3:6.0f} GB/s", flush=True)
+    kernels.check_status(status)
+
+
 def bench_float32() -> None:
     """The kernels of the true 32-bit path at SmolLM2-135M shapes: FMA products for a 2,048-token prompt and for 8
     decoded rows, split-key decode attention and one-warp-per-row attention over a float32 cache."""
@@ -445,7 +574,7 @@ def bench_layer_gemms(rows) -> None:
     kernels.check_status(st)
 
 
-CASES = ("gemm_stream", "gemm_tc", "attention_decode", "attention_splits", "attention_prefill", "float32", "small", "decode_program", "layer_gemms", "latent_attention", "delta_rule")
+CASES = ("gemm_stream", "gemm_tc", "attention_decode", "attention_splits", "attention_prefill", "float32", "small", "decode_program", "layer_gemms", "latent_attention", "delta_rule", "lonorax")
 
 
 def main(argv) -> int:
@@ -479,6 +608,8 @@ def main(argv) -> int:
         bench_latent_attention()
     elif argv[0] == "delta_rule":
         bench_delta_rule()
+    elif argv[0] == "lonorax":
+        bench_lonorax()
     else:
         bench_attention_prefill()
     return 0
