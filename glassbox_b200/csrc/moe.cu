@@ -15,7 +15,7 @@
 #include <math.h>
 
 constexpr int MOE_MAX_EXPERTS = 512;
-constexpr int MOE_ROUTE_THREADS = 128;
+constexpr int MOE_ROUTE_THREADS = 1024;      // at most; the launch takes a warp per expert (and one for the shared gate)
 
 __device__ __forceinline__ float moe_sigmoid(float v) { return 1.0f / (1.0f + expf(-v)); }
 
@@ -92,9 +92,9 @@ __global__ void __launch_bounds__(MOE_ROUTE_THREADS) moe_route_kernel(
     if (row >= n || positions[row] < 0) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const T* src = h + (size_t)row * d;
-    for (int i = threadIdx.x; i < d; i += MOE_ROUTE_THREADS) hx[i] = gb_to_float(src[i]);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) hx[i] = gb_to_float(src[i]);
     __syncthreads();
-    for (int e = warp; e < E + (w_gate ? 1 : 0); e += MOE_ROUTE_THREADS / 32) {
+    for (int e = warp; e < E + (w_gate ? 1 : 0); e += (int)(blockDim.x >> 5)) {
         if (e < E) {
             const float z = moe_warp_dot<float>(w_router + (size_t)e * d, hx, d, lane);
             if (lane == 0) {
@@ -154,14 +154,17 @@ GB_EXPORT int gb_moe_route(const void* h, int h_dtype, int d, const float* w_rou
     GB_REQUIRE(w_gate == nullptr || gate_out != nullptr, "gb_moe_route: a gate needs its output");
     if (n == 0) return 0;
     const size_t smem = (size_t)d * 4;
+    int warps = E + (w_gate ? 1 : 0);
+    warps = warps < 4 ? 4 : (warps > MOE_ROUTE_THREADS / 32 ? MOE_ROUTE_THREADS / 32 : warps);
+    const dim3 block(32 * warps);
     if (h_dtype == GB_F32) {
         if (smem > 32 * 1024) cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        gb_launch(GB_PDL_ELEMENTWISE, moe_route_kernel<float>, dim3(n), dim3(MOE_ROUTE_THREADS), smem, stream, (const float*)h, d, w_router,
+        gb_launch(GB_PDL_ELEMENTWISE, moe_route_kernel<float>, dim3(n), block, smem, stream, (const float*)h, d, w_router,
                   correction, w_gate, positions, n, E, top, groups, keep, route_scale, choice_out, weight_out, gate_out);
     } else if (h_dtype == GB_BF16) {
         if (smem > 32 * 1024)
             cudaFuncSetAttribute(moe_route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        gb_launch(GB_PDL_ELEMENTWISE, moe_route_kernel<__nv_bfloat16>, dim3(n), dim3(MOE_ROUTE_THREADS), smem, stream,
+        gb_launch(GB_PDL_ELEMENTWISE, moe_route_kernel<__nv_bfloat16>, dim3(n), block, smem, stream,
                   (const __nv_bfloat16*)h, d, w_router, correction, w_gate, positions, n, E, top, groups, keep, route_scale, choice_out,
                   weight_out, gate_out);
     } else {
@@ -339,11 +342,13 @@ GB_EXPORT int gb_moe_expert_halves(const void* h, int dtype, int d, const void* 
 //   moe_sort            one block: counts per expert, where each expert's pairs start (offsets [E + 1]), where its 64-row
 //                       tiles start (tile_start [E + 1]), and sorted[slot] = pair. The order of an expert's pairs is not
 //                       fixed from run to run; no result depends on it (a pair's numbers do not depend on its slot).
-//   moe_grouped_gemm    a block = 64 slots of one expert x 64 outputs, 4 warps of mma.sync m16n8k16 (bf16, float32 sums),
-//                       operands staged by cp.async in two buffers. UP: rows of h gathered by pair, epilogue relu^2, act
+//   moe_grouped_gemm    a block = 64 slots of one expert x 128 outputs, 4 warps of mma.sync m16n8k16 (bf16, float32 sums),
+//                       operands staged by cp.async in a ring of three buffers of 64 columns. UP: rows of h gathered by pair, epilogue relu^2, act
 //                       [slot, ff] bfloat16. DOWN: rows of act, float32 out scattered to pair[pair, :].
 // ----------------------------------------------------------------------------------------------
-constexpr int MG_BM = 64, MG_BN = 64, MG_BK = 32, MG_LD = MG_BK + 8;     // (rows padded by 16 bytes: ldmatrix meets no bank twice)
+constexpr int MG_BM = 64, MG_BN = 128, MG_BK = 64, MG_STAGES = 3;
+constexpr int MG_LD = MG_BK + 8;             // (rows padded by 16 bytes: ldmatrix meets no bank twice)
+constexpr int MG_SMEM = MG_STAGES * (MG_BM + MG_BN) * MG_LD * 2;
 
 __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ choice, const int* __restrict__ positions, int n, int E,
                                                         int top, int* __restrict__ offsets, int* __restrict__ tile_start,
@@ -390,7 +395,9 @@ __global__ void __launch_bounds__(128) moe_grouped_gemm_kernel(const __nv_bfloat
                                                                const int* __restrict__ sorted, const int* __restrict__ offsets,
                                                                const int* __restrict__ tile_start, int E, int top,
                                                                void* __restrict__ C, long long ldc) {
-    __shared__ __align__(16) __nv_bfloat16 sa[2][MG_BM][MG_LD], sb[2][MG_BN][MG_LD];
+    extern __shared__ __align__(16) unsigned char mg_smem[];
+    __nv_bfloat16* sa = reinterpret_cast<__nv_bfloat16*>(mg_smem);                 // [stages][BM][LD]
+    __nv_bfloat16* sb = sa + MG_STAGES * MG_BM * MG_LD;                            // [stages][BN][LD]
     __shared__ int src_row[MG_BM];           // where each slot's input row is (UP: the token's row; DOWN: the slot), -1: none
     __shared__ int dst_row[MG_BM];           // where its output goes (UP: the slot; DOWN: the pair)
     gb_pdl_launch_dependents();
@@ -415,64 +422,68 @@ __global__ void __launch_bounds__(128) moe_grouped_gemm_kernel(const __nv_bfloat
     }
     __syncthreads();
     const __nv_bfloat16* Wb = W + (size_t)e * N * K;
-    // staging: 64 rows x 32 columns = 256 chunks of 16 bytes per operand; a thread takes two of each
-    auto stage = [&](int buf, int k0) {
+    const int steps = (K + MG_BK - 1) / MG_BK;
+    // staging: rows of BK = 64 columns are 8 chunks of 16 bytes; 128 threads take 4 chunks of A and 8 of W each
+    auto stage = [&](int st) {
+        if (st < steps) {
+            const int buf = st % MG_STAGES, k0 = st * MG_BK;
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int chunk = tid + i * 128, r = chunk >> 2, c = (chunk & 3) * 8;
-            const int ar = src_row[r];
-            const bool ka = k0 + c < K;
-            const int kc = ka ? k0 + c : 0;          // (an address that exists even where nothing is read)
-            mg_cp_async16(&sa[buf][r][c], A + (size_t)(ar < 0 ? 0 : ar) * lda + kc, ar >= 0 && ka);
-            const int br = n0 + r;
-            mg_cp_async16(&sb[buf][r][c], Wb + (size_t)(br < N ? br : 0) * K + kc, br < N && ka);
+            for (int i = 0; i < (MG_BM * 8) / 128; ++i) {
+                const int chunk = tid + i * 128, r = chunk >> 3, c = (chunk & 7) * 8;
+                const int ar = src_row[r];
+                const bool ka = k0 + c < K;
+                mg_cp_async16(sa + (buf * MG_BM + r) * MG_LD + c, A + (size_t)(ar < 0 ? 0 : ar) * lda + (ka ? k0 + c : 0), ar >= 0 && ka);
+            }
+#pragma unroll
+            for (int i = 0; i < (MG_BN * 8) / 128; ++i) {
+                const int chunk = tid + i * 128, r = chunk >> 3, c = (chunk & 7) * 8;
+                const int br = n0 + r;
+                const bool ka = k0 + c < K;
+                mg_cp_async16(sb + (buf * MG_BN + r) * MG_LD + c, Wb + (size_t)(br < N ? br : 0) * K + (ka ? k0 + c : 0), br < N && ka);
+            }
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");      // (a group per round, empty past the end: the count stays in step)
     };
-    const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;       // this warp's 32 x 32 piece of the tile
-    float acc[2][4][4];
+    const int wm = (warp >> 1) * 32, wn = (warp & 1) * 64;       // this warp's 32 x 64 piece of the tile
+    float acc[2][8][4];
 #pragma unroll
     for (int i = 0; i < 2; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < 8; ++j)
 #pragma unroll
             for (int t = 0; t < 4; ++t) acc[i][j][t] = 0.f;
-    const int steps = (K + MG_BK - 1) / MG_BK;
-    stage(0, 0);
+#pragma unroll
+    for (int st = 0; st < MG_STAGES - 1; ++st) stage(st);
     for (int s = 0; s < steps; ++s) {
-        if (s + 1 < steps) {
-            stage((s + 1) & 1, (s + 1) * MG_BK);
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
-        } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-        }
-        __syncthreads();
-        const int buf = s & 1;
+        asm volatile("cp.async.wait_group %0;" ::"n"(MG_STAGES - 2) : "memory");
+        __syncthreads();                     // round s has landed for everyone, and everyone is done with round s - 1's buffer
+        stage(s + MG_STAGES - 1);
+        const __nv_bfloat16* ta = sa + (s % MG_STAGES) * MG_BM * MG_LD;
+        const __nv_bfloat16* tb = sb + (s % MG_STAGES) * MG_BN * MG_LD;
 #pragma unroll
         for (int kk = 0; kk < MG_BK; kk += 16) {
-            unsigned a[2][4], b[4][2];
+            unsigned a[2][4], b[8][2];
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
-                const unsigned addr = (unsigned)__cvta_generic_to_shared(&sa[buf][wm + i * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+                const unsigned addr = (unsigned)__cvta_generic_to_shared(ta + (wm + i * 16 + (lane & 15)) * MG_LD + kk + (lane >> 4) * 8);
                 asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                              : "=r"(a[i][0]), "=r"(a[i][1]), "=r"(a[i][2]), "=r"(a[i][3]) : "r"(addr));
             }
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {      // two 8-column tiles of W per ldmatrix.x4: rows n, columns k
+            for (int j = 0; j < 4; ++j) {      // two 8-column tiles of W per ldmatrix.x4: rows n, columns k
                 const int nrow = wn + j * 16 + (lane & 7) + ((lane >> 4) << 3), kcol = kk + ((lane >> 3) & 1) * 8;
-                const unsigned addr = (unsigned)__cvta_generic_to_shared(&sb[buf][nrow][kcol]);
+                const unsigned addr = (unsigned)__cvta_generic_to_shared(tb + nrow * MG_LD + kcol);
                 asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                              : "=r"(b[2 * j][0]), "=r"(b[2 * j][1]), "=r"(b[2 * j + 1][0]), "=r"(b[2 * j + 1][1]) : "r"(addr));
             }
 #pragma unroll
             for (int i = 0; i < 2; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
+                for (int j = 0; j < 8; ++j)
                     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                                  : "+f"(acc[i][j][0]), "+f"(acc[i][j][1]), "+f"(acc[i][j][2]), "+f"(acc[i][j][3])
                                  : "r"(a[i][0]), "r"(a[i][1]), "r"(a[i][2]), "r"(a[i][3]), "r"(b[j][0]), "r"(b[j][1]));
         }
-        __syncthreads();
     }
     // epilogue: thread holds rows (lane / 4) and (lane / 4 + 8) of each 16-row tile, columns 2 * (lane % 4), + 1
 #pragma unroll
@@ -483,7 +494,7 @@ __global__ void __launch_bounds__(128) moe_grouped_gemm_kernel(const __nv_bfloat
             const int out_row = dst_row[r];
             if (out_row < 0) continue;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < 8; ++j) {
                 const int col = n0 + wn + j * 8 + (lane & 3) * 2;
                 float v0 = acc[i][j][half * 2], v1 = acc[i][j][half * 2 + 1];
                 if (UP) {
@@ -521,11 +532,13 @@ GB_EXPORT int gb_moe_grouped_gemm(const void* a, long long lda, const void* w, i
     GB_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0, "gb_moe_grouped_gemm: operands must be 16-byte aligned");
     if (pairs == 0) return 0;
     dim3 grid(gb_ceil_div(pairs, MG_BM) + E, gb_ceil_div(N, MG_BN));      // (at most this many tiles: blocks beyond the last return)
+    cudaFuncSetAttribute(moe_grouped_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, MG_SMEM);
+    cudaFuncSetAttribute(moe_grouped_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, MG_SMEM);
     if (up)
-        gb_launch(GB_PDL_GEMM, moe_grouped_gemm_kernel<true>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)a, lda,
+        gb_launch(GB_PDL_GEMM, moe_grouped_gemm_kernel<true>, grid, dim3(128), MG_SMEM, stream, (const __nv_bfloat16*)a, lda,
                   (const __nv_bfloat16*)w, N, K, sorted, offsets, tile_start, E, top, c, ldc);
     else
-        gb_launch(GB_PDL_GEMM, moe_grouped_gemm_kernel<false>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)a, lda,
+        gb_launch(GB_PDL_GEMM, moe_grouped_gemm_kernel<false>, grid, dim3(128), MG_SMEM, stream, (const __nv_bfloat16*)a, lda,
                   (const __nv_bfloat16*)w, N, K, sorted, offsets, tile_start, E, top, c, ldc);
     return gb_check_launch("gb_moe_grouped_gemm");
 }

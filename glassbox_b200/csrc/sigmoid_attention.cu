@@ -229,28 +229,74 @@ GB_EXPORT int gb_sigmoid_attention_rows(const void* q, void* out, int dtype, con
 
 // ----------------------------------------------------------------------------------------------
 // Single decoded tokens: one block of 8 warps per (row, head). The warps take the row's visible keys 32 at a time in turn
-// (warp w the chunks w, w + 8, ...): a lane per key for the score, then a lane per pair of value channels for the sum, four
-// keys' loads in flight at once; the warps' partial sums meet in shared memory and are added in a fixed order. The order
-// of a row's sums depends on its position and the window alone. Value sizes must be even.
+// (warp w the chunks w, w + 8, ...). Per chunk a lane first looks up the page of "its" key; then the value rows of all 32
+// keys are asked for in 16-byte pieces (LPK lanes cover one key's row, so a warp-wide load fetches 32 / LPK keys, and all
+// LPK such loads are in flight together, before the scores exist: their addresses need only the page table); then the
+// lane's key row is read whole and dotted with the query, the weight sigmoid(score) formed in float32 and handed to the
+// lanes that hold that key's values. A lane sums its 16-byte piece of channels over its keys; at the end the lanes that
+// hold the same channels add up (shuffles), then the warps (shared memory, fixed order). The order of a row's sums
+// depends on its position and the window alone. A value row must be 64, 128, 256 or 512 bytes.
 // ----------------------------------------------------------------------------------------------
 constexpr int SAD_WARPS = 8;
 
-__device__ __forceinline__ float2 sad_load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
-__device__ __forceinline__ float2 sad_load2(const __nv_bfloat16* p) {
-    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+template <typename T> struct SadPiece;                 // 16 bytes of a value row as floats
+template <> struct SadPiece<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void unpack(const uint4& raw, float (&f)[4]) {
+        f[0] = __uint_as_float(raw.x); f[1] = __uint_as_float(raw.y); f[2] = __uint_as_float(raw.z); f[3] = __uint_as_float(raw.w);
+    }
+};
+template <> struct SadPiece<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void unpack(const uint4& raw, float (&f)[8]) {
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const float2 v = __bfloat1622float2(p[t]);
+            f[2 * t] = v.x;
+            f[2 * t + 1] = v.y;
+        }
+    }
+};
+
+// q . k for R query heads at once (q: R rows of D floats in shared memory), the key row read once
+template <typename T, int R>
+__device__ __forceinline__ void sad_dots(const float* __restrict__ q, const T* __restrict__ k, int D, float (&out)[R]) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) out[r] = 0.f;
+    constexpr int PN = SadPiece<T>::N;
+    if (D % PN == 0 && ((uintptr_t)k & 15) == 0) {
+#pragma unroll 16
+        for (int i = 0; i < D; i += PN) {          // (a key row's loads all in flight together: they are the critical path)
+            float f[PN];
+            SadPiece<T>::unpack(*reinterpret_cast<const uint4*>(k + i), f);
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+                for (int e = 0; e < PN; ++e) out[r] = fmaf(q[r * D + i + e], f[e], out[r]);
+        }
+    } else {
+        for (int i = 0; i < D; ++i) {
+            const float kv = gb_to_float(k[i]);
+#pragma unroll
+            for (int r = 0; r < R; ++r) out[r] = fmaf(q[r * D + i], kv, out[r]);
+        }
+    }
 }
 
-template <typename T>
+template <typename T, int LPK, int R>
 __global__ void __launch_bounds__(SAD_WARPS * 32) sigmoid_attention_decode_kernel(
     const T* __restrict__ q, T* __restrict__ out, const T* __restrict__ kcache, const T* __restrict__ vcache,
     const int* __restrict__ block_tables, int max_pages, const int* __restrict__ row_seq, const int* __restrict__ positions,
     const float* __restrict__ head_bias, int n, int H, int G, int D, int V, int page_size, long long num_pages, float scale,
     int window, int* __restrict__ status) {
-    __shared__ __align__(16) float qs[SA_MAX_DIM];
-    __shared__ float part[SAD_WARPS][SA_MAX_DIM];
+    constexpr int PN = SadPiece<T>::N;          // channels in a 16-byte piece
+    constexpr int KPI = 32 / LPK;               // keys that one warp-wide load fetches
+    __shared__ __align__(16) float qs[R * SA_MAX_DIM];        // the R heads' queries, D apart
+    __shared__ float part[SAD_WARPS][R * SA_MAX_DIM / (R > 2 ? 2 : 1)];      // (R > 2 only with value rows of up to 128 channels)
     gb_pdl_launch_dependents();
     gb_pdl_wait();
-    const int row = blockIdx.x, head = blockIdx.y;
+    const int row = blockIdx.x, head = blockIdx.y * R;        // R consecutive heads of one key/value group
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (row >= n) return;
     const int pos = positions[row];
@@ -262,62 +308,69 @@ __global__ void __launch_bounds__(SAD_WARPS * 32) sigmoid_attention_decode_kerne
     const int g = head / (H / G);
     const int* table = block_tables + (size_t)row_seq[row] * max_pages;
     const T* qrow = q + ((size_t)row * H + head) * D;
-    for (int i = threadIdx.x; i < D; i += SAD_WARPS * 32) qs[i] = gb_to_float(qrow[i]);
+    for (int i = threadIdx.x; i < R * D; i += SAD_WARPS * 32) qs[i] = gb_to_float(qrow[i]);
     __syncthreads();
-    const float bias = head_bias ? head_bias[head] : 0.f;
+    float bias[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) bias[r] = head_bias ? head_bias[head + r] : 0.f;
     const int first = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
     const int chunks = (pos - first) / 32 + 1;
-    constexpr int NJ = SA_MAX_DIM / 64;
-    float2 acc[NJ];
+    const int sub = lane / LPK, piece = lane % LPK;     // this lane holds piece `piece` of the keys sub, sub + KPI, ...
+    float acc[R][PN];
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) acc[j] = make_float2(0.f, 0.f);
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int c = 0; c < PN; ++c) acc[r][c] = 0.f;
     for (int c = warp; c < chunks; c += SAD_WARPS) {
         const int key = first + c * 32 + lane;
-        float p = 0.f;
         long long at = -1;
         if (key <= pos) {
             const long long page = table[key / page_size];
-            if (page < 0 || page >= num_pages) {
-                atomicOr(status, GB_STATUS_BAD_SLOT);
-            } else {
-                at = (page * G + g) * page_size + key % page_size;
-                const float sc = sa_dot<T>(qs, kcache + at * D, D) * scale + bias;
-                p = 1.0f / (1.0f + expf(-sc));
-            }
+            if (page < 0 || page >= num_pages) atomicOr(status, GB_STATUS_BAD_SLOT);
+            else at = (page * G + g) * page_size + key % page_size;
         }
-#pragma unroll 2
-        for (int t0 = 0; t0 < 32; t0 += 4) {
-            float pt[4];
-            float2 val[4][NJ];
+        uint4 raw[LPK];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                pt[u] = __shfl_sync(0xffffffffu, p, t0 + u);
-                const long long vr = __shfl_sync(0xffffffffu, at, t0 + u);
+        for (int r = 0; r < LPK; ++r) {
+            const long long vr = __shfl_sync(0xffffffffu, at, r * KPI + sub);
+            raw[r] = vr >= 0 ? *reinterpret_cast<const uint4*>(vcache + vr * V + piece * PN) : make_uint4(0u, 0u, 0u, 0u);
+        }
+        float p[R];
 #pragma unroll
-                for (int j = 0; j < NJ; ++j) {
-                    const int i = 2 * lane + 64 * j;
-                    val[u][j] = (vr >= 0 && i < V) ? sad_load2(vcache + vr * V + i) : make_float2(0.f, 0.f);
-                }
+        for (int r = 0; r < R; ++r) p[r] = 0.f;
+        if (at >= 0) {
+            float sc[R];
+            sad_dots<T, R>(qs, kcache + at * D, D, sc);
+#pragma unroll
+            for (int r = 0; r < R; ++r) p[r] = 1.0f / (1.0f + expf(-(sc[r] * scale + bias[r])));
+        }
+#pragma unroll
+        for (int v = 0; v < LPK; ++v) {
+            float f[PN];
+            SadPiece<T>::unpack(raw[v], f);
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const float pt = __shfl_sync(0xffffffffu, p[r], v * KPI + sub);
+#pragma unroll
+                for (int e = 0; e < PN; ++e) acc[r][e] = fmaf(pt, f[e], acc[r][e]);
             }
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-#pragma unroll
-                for (int j = 0; j < NJ; ++j) {
-                    acc[j].x = fmaf(pt[u], val[u][j].x, acc[j].x);
-                    acc[j].y = fmaf(pt[u], val[u][j].y, acc[j].y);
-                }
         }
     }
+    // lanes with the same piece hold sums over different keys: add them (fixed order), then the warps
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-        const int i = 2 * lane + 64 * j;
-        if (i < V) {
-            part[warp][i] = acc[j].x;
-            part[warp][i + 1] = acc[j].y;
-        }
+    for (int o = LPK; o < 32; o <<= 1)
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int e = 0; e < PN; ++e) acc[r][e] += __shfl_xor_sync(0xffffffffu, acc[r][e], o);
+    if (sub == 0) {
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int e = 0; e < PN; ++e) part[warp][r * V + piece * PN + e] = acc[r][e];
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < V; i += SAD_WARPS * 32) {
+    for (int i = threadIdx.x; i < R * V; i += SAD_WARPS * 32) {      // (the R heads' outputs are neighbours: head * V + channel)
         float t = 0.f;
 #pragma unroll
         for (int w = 0; w < SAD_WARPS; ++w) t += part[w][i];
@@ -325,26 +378,46 @@ __global__ void __launch_bounds__(SAD_WARPS * 32) sigmoid_attention_decode_kerne
     }
 }
 
+// 1 if the decode kernel takes value rows of this many bytes
+GB_EXPORT int gb_sigmoid_attention_decode_supported(int value_row_bytes) {
+    return value_row_bytes == 64 || value_row_bytes == 128 || value_row_bytes == 256 || value_row_bytes == 512 ? 1 : 0;
+}
+
+template <typename T>
+static int sad_launch(const void* q, void* out, const void* kcache, const void* vcache, const int* block_tables, int max_pages,
+                      const int* row_seq, const int* positions, const float* head_bias, int n, int H, int G, int D, int V, int page_size,
+                      long long num_pages, float scale, int window, int* status, cudaStream_t stream) {
+    const int lpk = V * (int)sizeof(T) / 16;
+    // With enough (row, key/value head) pairs to fill the GPU, the query heads of a group go four at a time through one
+    // block, which then reads the group's keys and values once for the four; with few rows every head gets its own block.
+    const int group = H / G;
+    const bool together = group % 4 == 0 && V <= 128 && lpk <= 16 && (long long)n * (H / 4) >= 148;
+#define SAD_CASE(L, RR)                                                                                                                  \
+    if (lpk == L && (together ? 4 : 1) == RR)                                                                                            \
+        gb_launch(GB_PDL_ATTENTION, sigmoid_attention_decode_kernel<T, L, RR>, dim3(n, H / RR), dim3(SAD_WARPS * 32), 0, stream,         \
+                  (const T*)q, (T*)out, (const T*)kcache, (const T*)vcache, block_tables, max_pages, row_seq, positions, head_bias, n, H, \
+                  G, D, V, page_size, num_pages, scale, window, status);
+    SAD_CASE(4, 1) SAD_CASE(8, 1) SAD_CASE(16, 1) SAD_CASE(32, 1) SAD_CASE(4, 4) SAD_CASE(8, 4) SAD_CASE(16, 4)
+#undef SAD_CASE
+    return gb_check_launch("gb_sigmoid_attention_decode");
+}
+
 GB_EXPORT int gb_sigmoid_attention_decode(const void* q, void* out, int dtype, const void* kcache, const void* vcache,
                                           const int* block_tables, int max_pages, const int* row_seq, const int* positions,
                                           const float* head_bias, int n, int H, int G, int D, int V, int page_size, long long num_pages,
                                           float scale, int window, int* status, cudaStream_t stream) {
     GB_REQUIRE(n >= 0 && H > 0 && G > 0 && H % G == 0, "gb_sigmoid_attention_decode: heads %d must be a multiple of kv heads %d", H, G);
-    GB_REQUIRE(D > 0 && D <= SA_MAX_DIM && V > 0 && V <= SA_MAX_DIM && V % 2 == 0,
-               "gb_sigmoid_attention_decode: head sizes %d / %d (values: even) are outside 1..%d", D, V, SA_MAX_DIM);
+    GB_REQUIRE(dtype == GB_F32 || dtype == GB_BF16, "gb_sigmoid_attention_decode: unsupported dtype %d", dtype);
+    GB_REQUIRE(D > 0 && D <= SA_MAX_DIM && V > 0 && V <= SA_MAX_DIM && gb_sigmoid_attention_decode_supported(V * (dtype == GB_F32 ? 4 : 2)),
+               "gb_sigmoid_attention_decode: head sizes %d / %d are not built (a value row must be 64, 128, 256 or 512 bytes)", D, V);
     GB_REQUIRE(page_size > 0 && max_pages > 0 && window >= 0, "gb_sigmoid_attention_decode: bad page geometry or window");
+    GB_REQUIRE(((uintptr_t)vcache & 15) == 0, "gb_sigmoid_attention_decode: the value cache must be 16-byte aligned");
     if (n == 0) return 0;
     if (dtype == GB_F32)
-        gb_launch(GB_PDL_ATTENTION, sigmoid_attention_decode_kernel<float>, dim3(n, H), dim3(SAD_WARPS * 32), 0, stream, (const float*)q,
-                  (float*)out, (const float*)kcache, (const float*)vcache, block_tables, max_pages, row_seq, positions, head_bias, n, H,
-                  G, D, V, page_size, num_pages, scale, window, status);
-    else if (dtype == GB_BF16)
-        gb_launch(GB_PDL_ATTENTION, sigmoid_attention_decode_kernel<__nv_bfloat16>, dim3(n, H), dim3(SAD_WARPS * 32), 0, stream,
-                  (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, block_tables,
-                  max_pages, row_seq, positions, head_bias, n, H, G, D, V, page_size, num_pages, scale, window, status);
-    else
-        GB_REQUIRE(false, "gb_sigmoid_attention_decode: unsupported dtype %d", dtype);
-    return gb_check_launch("gb_sigmoid_attention_decode");
+        return sad_launch<float>(q, out, kcache, vcache, block_tables, max_pages, row_seq, positions, head_bias, n, H, G, D, V, page_size,
+                                 num_pages, scale, window, status, stream);
+    return sad_launch<__nv_bfloat16>(q, out, kcache, vcache, block_tables, max_pages, row_seq, positions, head_bias, n, H, G, D, V,
+                                     page_size, num_pages, scale, window, status, stream);
 }
 
 // ----------------------------------------------------------------------------------------------
@@ -399,16 +472,18 @@ __global__ void __launch_bounds__(128) sigmoid_attention_tiles_kernel(
         sat_cp16(sq + r * LDK + c, q + ((size_t)(row0 + (r < rows ? r : 0)) * H + head) * D + c, r < rows);
     }
     auto stage = [&](int buf, int kb) {
-        // a thread looks up the page of the keys it copies: 64 keys x (D + V) / 8 chunks over 128 threads
-        for (int chunk = tid; chunk < SAT_BN * ((D + V) / 8); chunk += 128) {
-            const int key = chunk / ((D + V) / 8), c = (chunk % ((D + V) / 8)) * 8;
-            const int kk = kb + key;
-            long long page = kk <= p_hi ? table[kk / page_size] : -1;
-            if (kk <= p_hi && (page < 0 || page >= num_pages)) {
-                atomicOr(status, GB_STATUS_BAD_SLOT);
-                page = -1;
-            }
-            const long long at = page < 0 ? 0 : (page * G + g) * page_size + kk % page_size;
+        // two threads per key: one page look-up each, then half of the key's 16-byte pieces (key row, then value row)
+        constexpr int CPK = (D + V) / 8;
+        const int key = tid >> 1, kk = kb + key;
+        long long page = kk <= p_hi ? table[kk / page_size] : -1;
+        if (kk <= p_hi && (page < 0 || page >= num_pages)) {
+            atomicOr(status, GB_STATUS_BAD_SLOT);
+            page = -1;
+        }
+        const long long at = page < 0 ? 0 : (page * G + g) * page_size + kk % page_size;
+#pragma unroll
+        for (int i = 0; i < CPK / 2; ++i) {
+            const int c = ((tid & 1) * (CPK / 2) + i) * 8;
             if (c < D) sat_cp16(sk + (buf * SAT_BN + key) * LDK + c, kcache + at * D + c, page >= 0);
             else sat_cp16(sv + (buf * SAT_BN + key) * LDV + (c - D), vcache + at * V + (c - D), page >= 0);
         }
@@ -464,17 +539,23 @@ __global__ void __launch_bounds__(128) sigmoid_attention_tiles_kernel(
                                  : "r"(qf[kd][0]), "r"(qf[kd][1]), "r"(qf[kd][2]), "r"(qf[kd][3]), "r"(b2), "r"(b3));
                 }
             }
-            // weights: float32 sigmoid, the causal edge and the window per element
+            // weights: float32 sigmoid; the causal edge and the window per element, except in tiles that every row of the
+            // warp sees whole (most of them)
+            const bool whole = kb + SAT_BN - 1 <= w_lo && (window <= 0 || w_hi - kb < window) && w_hi <= p_hi;
+            const float c1 = -scale * 1.4426950408889634f, c0 = -bias * 1.4426950408889634f;     // exp(-(s * scale + bias)) = 2^(s c1 + c0)
             unsigned pf[SAT_BN / 16][4];
 #pragma unroll
             for (int j = 0; j < SAT_BN / 8; ++j) {
                 float p[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const int key = kb + j * 8 + (lane & 3) * 2 + (e & 1);
-                    const int pos = e < 2 ? my_pos0 : my_pos1;
-                    const bool sees = key <= pos && (window <= 0 || pos - key < window) && pos <= p_hi;
-                    p[e] = sees ? __fdividef(1.0f, 1.0f + __expf(-(s[j][e] * scale + bias))) : 0.f;      // (rounded to bfloat16 next)
+                    p[e] = __fdividef(1.0f, 1.0f + exp2f(fmaf(s[j][e], c1, c0)));      // (rounded to bfloat16 next)
+                    if (!whole) {
+                        const int key = kb + j * 8 + (lane & 3) * 2 + (e & 1);
+                        const int pos = e < 2 ? my_pos0 : my_pos1;
+                        const bool sees = key <= pos && (window <= 0 || pos - key < window) && pos <= p_hi;
+                        p[e] = sees ? p[e] : 0.f;
+                    }
                 }
                 const __nv_bfloat162 lo = __floats2bfloat162_rn(p[0], p[1]), hi = __floats2bfloat162_rn(p[2], p[3]);
                 pf[j >> 1][(j & 1) * 2] = *reinterpret_cast<const unsigned*>(&lo);

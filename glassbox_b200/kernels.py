@@ -97,6 +97,7 @@ _SIGNATURES = {
     "gb_qk_norm_rope_write": [_P, _LL, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _LL, _I, _P, _P],
     "gb_sigmoid_attention_rows": [_P, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
     "gb_sigmoid_attention_decode": [_P, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
+    "gb_sigmoid_attention_decode_supported": [_I],
     "gb_sigmoid_attention_tiles_supported": [_I, _I],
     "gb_sigmoid_attention_tiles": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
     "gb_mingru_scan": [_P, _LL, _P, _P, _P, _LL, _LL, _P, _LL, _I, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
@@ -1166,15 +1167,20 @@ def sigmoid_attention_rows(q: torch.Tensor, out: torch.Tensor, kcache: torch.Ten
           kcache.shape[0], float(scale), int(window) if window else 0, _ptr(status), _stream())
 
 
+def sigmoid_attention_decode_supported(dtype: torch.dtype, vdim: int) -> bool:
+    return dtype in _DT and bool(lib().gb_sigmoid_attention_decode_supported(vdim * (4 if dtype == torch.float32 else 2)))
+
+
 def sigmoid_attention_decode(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
                              row_seq: torch.Tensor, positions: torch.Tensor, head_bias: Optional[torch.Tensor], heads: int, kv_heads: int,
                              dim: int, vdim: int, page_size: int, scale: float, window: Optional[int], status: torch.Tensor) -> None:
     """``sigmoid_attention_rows`` for single decoded tokens: a block of eight warps per (row, head) that share the row's
-    keys and add their partial sums in a fixed order; ``vdim`` must be even."""
+    keys and add their partial sums in a fixed order; a value row must be 64, 128, 256 or 512 bytes
+    (``sigmoid_attention_decode_supported``)."""
     _cuda(q, out, kcache, vcache, block_tables, row_seq, positions, head_bias, status)
     n = q.shape[0]
     assert q.shape == (n, heads * dim) and out.shape == (n, heads * vdim) and q.is_contiguous() and out.is_contiguous()
-    assert q.dtype == out.dtype == kcache.dtype == vcache.dtype and block_tables.is_contiguous() and vdim % 2 == 0
+    assert q.dtype == out.dtype == kcache.dtype == vcache.dtype and block_tables.is_contiguous()
     assert head_bias is None or (head_bias.dtype == torch.float32 and head_bias.numel() == heads)
     _call("gb_sigmoid_attention_decode", _ptr(q), _ptr(out), _dt(q), _ptr(kcache), _ptr(vcache), _ptr(block_tables),
           block_tables.shape[1], _ptr(row_seq), _ptr(positions), _ptr(head_bias), n, heads, kv_heads, dim, vdim, page_size,

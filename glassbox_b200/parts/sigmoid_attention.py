@@ -77,7 +77,7 @@ class SigmoidAttention(Mixer):
         """Single decoded tokens take the kernel that shares a row's keys between the warps of a block; prompt portions in
         bfloat16 at head sizes the tile kernel is built for run on the tensor cores; everything else (float32 portions,
         other sizes) takes the one-warp-per-(row, head) kernel."""
-        if ctx.decode_only and self.V % 2 == 0:
+        if ctx.decode_only and kernels.sigmoid_attention_decode_supported(q.dtype, self.V):
             kernels.sigmoid_attention_decode(q, att, cache.k, cache.v, cache.block_tables, ctx.row_seq, ctx.positions,
                                              self.params.get("head_bias"), self.H, self.G, self.D, self.V, cache.page_size,
                                              self.spec.scale, self.spec.window, ctx.status)

@@ -167,7 +167,7 @@ def test_sigmoid_attention_kernels(dtype, H, G, D, V, rot, window, page):
         positions, row_seq = _i32([p for _, p in rows]), _i32([i for i, (r, k) in enumerate(step) for _ in range(k)])
         kernels.qk_norm_rope_write(x, _f32(gq), _f32(gk), inv, positions, cache.slots(rows), q, cache.k, cache.v, H, G, D, V, rot, eps,
                                    page, True, status)
-        single = all(k == 1 for _, k in step) and V % 2 == 0          # single tokens: the kernel that decoding uses
+        single = all(k == 1 for _, k in step) and kernels.sigmoid_attention_decode_supported(dtype, V)   # the kernel that decoding uses
         attend = kernels.sigmoid_attention_decode if single else kernels.sigmoid_attention_rows
         attend(q, out, cache.k, cache.v, cache.table([r for r, _ in step]), row_seq, positions, _f32(pb), H, G, D, V, page, scale, window,
                status)
@@ -274,13 +274,46 @@ def test_which_keys_a_tile_of_rows_sees(window, page):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_many_single_tokens_share_a_groups_keys(dtype):
+    """With many rows the decode kernel takes the four query heads of a key/value group through one block. 80 requests of
+    unequal length, one token each: every row against the plain sum over its own keys."""
+    from glassbox_b200 import kernels
+    rng = np.random.default_rng(9)
+    H, G, D, V, page, window, n = 8, 2, 32, 64, 16, 37, 80
+    lengths = [int(x) for x in rng.integers(1, 120, n)]
+    cache = _PagedRequests(lengths, G, D, V, page, dtype, seed=1)
+    cache.k.copy_(torch.randn(cache.k.shape, device=DEV))
+    cache.v.copy_(torch.randn(cache.v.shape, device=DEV))
+    q = torch.randn((n, H * D), device=DEV).to(dtype)
+    pb = rng.standard_normal(H) - 1.0
+    out = torch.zeros((n, H * V), dtype=dtype, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    positions = [L - 1 for L in lengths]
+    kernels.sigmoid_attention_decode(q, out, cache.k, cache.v, cache.table(list(range(n))), _i32(list(range(n))), _i32(positions), _f32(pb),
+                                     H, G, D, V, page, 0.3, window, status)
+    assert int(status.item()) == 0
+    got = out.float().cpu().numpy().reshape(n, H, V)
+    k64, v64, q64 = cache.k.float().cpu().numpy().astype(np.float64), cache.v.float().cpu().numpy().astype(np.float64), \
+        q.float().cpu().numpy().astype(np.float64).reshape(n, H, D)
+    for r in range(n):
+        want = np.zeros((H, V))
+        for j in range(lengths[r]):
+            if plain.visible(positions[r], j, window):
+                pg, off = cache.tables[r][j // page], j % page
+                for h in range(H):
+                    want[h] += plain.logistic(q64[r, h] @ k64[pg, h // (H // G), off] * 0.3 + pb[h]) * v64[pg, h // (H // G), off]
+        tol = 1e-4 if dtype == torch.float32 else 0.03
+        assert np.abs(got[r] - want).max() <= tol * max(1.0, np.abs(want).max()), f"row {r}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("window, page", [(5, 16), (16, 16), (17, 16), (40, 8), (None, 16)])
 def test_which_keys_a_row_sees(dtype, window, page):
     """Crafted cache: every key has the same direction as every query, so that every visible key weighs sigmoid(large) = 1
     exactly, and the value of key j is 2^(j mod 8) in channel j / 8: the output then spells out, bit by bit, which keys were
     summed. Rows at page borders, at the first positions, just inside and just outside the window, 300 keys back."""
     from glassbox_b200 import kernels
-    D, V, T = 16, 48, 330
+    D, V, T = 16, 64, 330
     cache = _PagedRequests([T], 1, D, V, page, dtype, seed=3)
     k = np.zeros((T, D)); k[:, 0] = 8.0
     v = np.zeros((T, V))
