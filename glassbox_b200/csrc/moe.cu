@@ -342,13 +342,14 @@ GB_EXPORT int gb_moe_expert_halves(const void* h, int dtype, int d, const void* 
 //   moe_sort            one block: counts per expert, where each expert's pairs start (offsets [E + 1]), where its 64-row
 //                       tiles start (tile_start [E + 1]), and sorted[slot] = pair. The order of an expert's pairs is not
 //                       fixed from run to run; no result depends on it (a pair's numbers do not depend on its slot).
-//   moe_grouped_gemm    a block = 64 slots of one expert x 128 outputs, 4 warps of mma.sync m16n8k16 (bf16, float32 sums),
+//   moe_grouped_gemm    a block = 64 slots of one expert x 128 outputs, 8 warps of mma.sync m16n8k16 (bf16, float32 sums),
 //                       operands staged by cp.async in a ring of three buffers of 64 columns. UP: rows of h gathered by pair, epilogue relu^2, act
 //                       [slot, ff] bfloat16. DOWN: rows of act, float32 out scattered to pair[pair, :].
 // ----------------------------------------------------------------------------------------------
 constexpr int MG_BM = 64, MG_BN = 128, MG_BK = 64, MG_STAGES = 3;
 constexpr int MG_LD = MG_BK + 8;             // (rows padded by 16 bytes: ldmatrix meets no bank twice)
 constexpr int MG_SMEM = MG_STAGES * (MG_BM + MG_BN) * MG_LD * 2;
+constexpr int MG_THREADS = 256;
 
 __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ choice, const int* __restrict__ positions, int n, int E,
                                                         int top, int* __restrict__ offsets, int* __restrict__ tile_start,
@@ -390,7 +391,7 @@ __device__ __forceinline__ void mg_cp_async16(void* smem, const void* gmem, bool
 }
 
 template <bool UP>
-__global__ void __launch_bounds__(128) moe_grouped_gemm_kernel(const __nv_bfloat16* __restrict__ A, long long lda,
+__global__ void __launch_bounds__(MG_THREADS) moe_grouped_gemm_kernel(const __nv_bfloat16* __restrict__ A, long long lda,
                                                                const __nv_bfloat16* __restrict__ W, int N, int K,
                                                                const int* __restrict__ sorted, const int* __restrict__ offsets,
                                                                const int* __restrict__ tile_start, int E, int top,
@@ -423,20 +424,20 @@ __global__ void __launch_bounds__(128) moe_grouped_gemm_kernel(const __nv_bfloat
     __syncthreads();
     const __nv_bfloat16* Wb = W + (size_t)e * N * K;
     const int steps = (K + MG_BK - 1) / MG_BK;
-    // staging: rows of BK = 64 columns are 8 chunks of 16 bytes; 128 threads take 4 chunks of A and 8 of W each
+    // staging: rows of BK = 64 columns are 8 chunks of 16 bytes; 256 threads take 2 chunks of A and 4 of W each
     auto stage = [&](int st) {
         if (st < steps) {
             const int buf = st % MG_STAGES, k0 = st * MG_BK;
 #pragma unroll
-            for (int i = 0; i < (MG_BM * 8) / 128; ++i) {
-                const int chunk = tid + i * 128, r = chunk >> 3, c = (chunk & 7) * 8;
+            for (int i = 0; i < (MG_BM * 8) / MG_THREADS; ++i) {
+                const int chunk = tid + i * MG_THREADS, r = chunk >> 3, c = (chunk & 7) * 8;
                 const int ar = src_row[r];
                 const bool ka = k0 + c < K;
                 mg_cp_async16(sa + (buf * MG_BM + r) * MG_LD + c, A + (size_t)(ar < 0 ? 0 : ar) * lda + (ka ? k0 + c : 0), ar >= 0 && ka);
             }
 #pragma unroll
-            for (int i = 0; i < (MG_BN * 8) / 128; ++i) {
-                const int chunk = tid + i * 128, r = chunk >> 3, c = (chunk & 7) * 8;
+            for (int i = 0; i < (MG_BN * 8) / MG_THREADS; ++i) {
+                const int chunk = tid + i * MG_THREADS, r = chunk >> 3, c = (chunk & 7) * 8;
                 const int br = n0 + r;
                 const bool ka = k0 + c < K;
                 mg_cp_async16(sb + (buf * MG_BN + r) * MG_LD + c, Wb + (size_t)(br < N ? br : 0) * K + (ka ? k0 + c : 0), br < N && ka);
@@ -444,12 +445,12 @@ __global__ void __launch_bounds__(128) moe_grouped_gemm_kernel(const __nv_bfloat
         }
         asm volatile("cp.async.commit_group;" ::: "memory");      // (a group per round, empty past the end: the count stays in step)
     };
-    const int wm = (warp >> 1) * 32, wn = (warp & 1) * 64;       // this warp's 32 x 64 piece of the tile
-    float acc[2][8][4];
+    const int wm = (warp >> 2) * 32, wn = (warp & 3) * 32;       // this warp's 32 x 32 piece of the tile (8 warps: 2 x 4)
+    float acc[2][4][4];
 #pragma unroll
     for (int i = 0; i < 2; ++i)
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int j = 0; j < 4; ++j)
 #pragma unroll
             for (int t = 0; t < 4; ++t) acc[i][j][t] = 0.f;
 #pragma unroll
@@ -462,7 +463,7 @@ __global__ void __launch_bounds__(128) moe_grouped_gemm_kernel(const __nv_bfloat
         const __nv_bfloat16* tb = sb + (s % MG_STAGES) * MG_BN * MG_LD;
 #pragma unroll
         for (int kk = 0; kk < MG_BK; kk += 16) {
-            unsigned a[2][4], b[8][2];
+            unsigned a[2][4], b[4][2];
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 const unsigned addr = (unsigned)__cvta_generic_to_shared(ta + (wm + i * 16 + (lane & 15)) * MG_LD + kk + (lane >> 4) * 8);
@@ -470,7 +471,7 @@ __global__ void __launch_bounds__(128) moe_grouped_gemm_kernel(const __nv_bfloat
                              : "=r"(a[i][0]), "=r"(a[i][1]), "=r"(a[i][2]), "=r"(a[i][3]) : "r"(addr));
             }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {      // two 8-column tiles of W per ldmatrix.x4: rows n, columns k
+            for (int j = 0; j < 2; ++j) {      // two 8-column tiles of W per ldmatrix.x4: rows n, columns k
                 const int nrow = wn + j * 16 + (lane & 7) + ((lane >> 4) << 3), kcol = kk + ((lane >> 3) & 1) * 8;
                 const unsigned addr = (unsigned)__cvta_generic_to_shared(tb + nrow * MG_LD + kcol);
                 asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -479,7 +480,7 @@ __global__ void __launch_bounds__(128) moe_grouped_gemm_kernel(const __nv_bfloat
 #pragma unroll
             for (int i = 0; i < 2; ++i)
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
+                for (int j = 0; j < 4; ++j)
                     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                                  : "+f"(acc[i][j][0]), "+f"(acc[i][j][1]), "+f"(acc[i][j][2]), "+f"(acc[i][j][3])
                                  : "r"(a[i][0]), "r"(a[i][1]), "r"(a[i][2]), "r"(a[i][3]), "r"(b[j][0]), "r"(b[j][1]));
@@ -494,7 +495,7 @@ __global__ void __launch_bounds__(128) moe_grouped_gemm_kernel(const __nv_bfloat
             const int out_row = dst_row[r];
             if (out_row < 0) continue;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < 4; ++j) {
                 const int col = n0 + wn + j * 8 + (lane & 3) * 2;
                 float v0 = acc[i][j][half * 2], v1 = acc[i][j][half * 2 + 1];
                 if (UP) {
@@ -535,10 +536,10 @@ GB_EXPORT int gb_moe_grouped_gemm(const void* a, long long lda, const void* w, i
     cudaFuncSetAttribute(moe_grouped_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, MG_SMEM);
     cudaFuncSetAttribute(moe_grouped_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, MG_SMEM);
     if (up)
-        gb_launch(GB_PDL_GEMM, moe_grouped_gemm_kernel<true>, grid, dim3(128), MG_SMEM, stream, (const __nv_bfloat16*)a, lda,
+        gb_launch(GB_PDL_GEMM, moe_grouped_gemm_kernel<true>, grid, dim3(MG_THREADS), MG_SMEM, stream, (const __nv_bfloat16*)a, lda,
                   (const __nv_bfloat16*)w, N, K, sorted, offsets, tile_start, E, top, c, ldc);
     else
-        gb_launch(GB_PDL_GEMM, moe_grouped_gemm_kernel<false>, grid, dim3(128), MG_SMEM, stream, (const __nv_bfloat16*)a, lda,
+        gb_launch(GB_PDL_GEMM, moe_grouped_gemm_kernel<false>, grid, dim3(MG_THREADS), MG_SMEM, stream, (const __nv_bfloat16*)a, lda,
                   (const __nv_bfloat16*)w, N, K, sorted, offsets, tile_start, E, top, c, ldc);
     return gb_check_launch("gb_moe_grouped_gemm");
 }

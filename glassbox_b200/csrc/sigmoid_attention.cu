@@ -259,6 +259,24 @@ template <> struct SadPiece<__nv_bfloat16> {
     }
 };
 
+// NP 16-byte pieces of a key row against the same channels of R queries (q rows D apart): all loads first, then the sums
+template <typename T, int R, int NP>
+__device__ __forceinline__ void sad_dot_pieces(const float* __restrict__ q, int D, const T* __restrict__ k, float (&out)[R]) {
+    constexpr int PN = SadPiece<T>::N;
+    uint4 raw[NP];
+#pragma unroll
+    for (int c = 0; c < NP; ++c) raw[c] = *reinterpret_cast<const uint4*>(k + c * PN);
+#pragma unroll
+    for (int c = 0; c < NP; ++c) {
+        float f[PN];
+        SadPiece<T>::unpack(raw[c], f);
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int e = 0; e < PN; ++e) out[r] = fmaf(q[r * D + c * PN + e], f[e], out[r]);
+    }
+}
+
 // q . k for R query heads at once (q: R rows of D floats in shared memory), the key row read once
 template <typename T, int R>
 __device__ __forceinline__ void sad_dots(const float* __restrict__ q, const T* __restrict__ k, int D, float (&out)[R]) {
@@ -266,15 +284,11 @@ __device__ __forceinline__ void sad_dots(const float* __restrict__ q, const T* _
     for (int r = 0; r < R; ++r) out[r] = 0.f;
     constexpr int PN = SadPiece<T>::N;
     if (D % PN == 0 && ((uintptr_t)k & 15) == 0) {
-#pragma unroll 16
-        for (int i = 0; i < D; i += PN) {          // (a key row's loads all in flight together: they are the critical path)
-            float f[PN];
-            SadPiece<T>::unpack(*reinterpret_cast<const uint4*>(k + i), f);
-#pragma unroll
-            for (int r = 0; r < R; ++r)
-#pragma unroll
-                for (int e = 0; e < PN; ++e) out[r] = fmaf(q[r * D + i + e], f[e], out[r]);
-        }
+        // a key row's loads are the critical path of a chunk: eight 16-byte pieces in flight together, then four, then single
+        int i = 0;
+        for (; i + 8 * PN <= D; i += 8 * PN) sad_dot_pieces<T, R, 8>(q + i, D, k + i, out);
+        for (; i + 4 * PN <= D; i += 4 * PN) sad_dot_pieces<T, R, 4>(q + i, D, k + i, out);
+        for (; i < D; i += PN) sad_dot_pieces<T, R, 1>(q + i, D, k + i, out);
     } else {
         for (int i = 0; i < D; ++i) {
             const float kv = gb_to_float(k[i]);

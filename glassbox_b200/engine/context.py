@@ -130,6 +130,9 @@ class StepContext:
         # A wiring over several residual streams leaves the fold of a branch's output into the streams to the kernel
         # that reads the streams next: (y, mix, write), see parts/block.py
         self.pending_fold = None
+        # ... and takes a branch output that is a weighted sum of rows as its parts (kernels.WeightedRows), if the part offers
+        self.accepts_weighted_rows = False
+        self.weighted_rows = None
 
     def scratch(self, name: str, shape, dtype: Optional[torch.dtype] = None, grow: bool = False) -> torch.Tensor:
         return (self._grow if grow else self._scratch).get(name, shape, dtype, grow)

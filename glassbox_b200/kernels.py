@@ -93,7 +93,7 @@ _SIGNATURES = {
                                 _I, _I, _P, _P, _LL, _P, _LL, _I, _I, _I, _I, _P, _P, _I, _P],
     "gb_short_conv_state": [_P, _LL, _P, _LL, _LL, _P, _P, _P, _I, _I, _I, _I, _P],
     "gb_streams_broadcast": [_P, _P, _I, _I, _I, _P],
-    "gb_streams_step": [_P, _I, _I, _P, _LL, _P, _P, _P, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _P],
+    "gb_streams_step": [_P, _I, _I, _P, _LL, _P, _P, _I, _P, _LL, _P, _P, _P, _P, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _P],
     "gb_qk_norm_rope_write": [_P, _LL, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _LL, _I, _P, _P],
     "gb_sigmoid_attention_rows": [_P, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
     "gb_sigmoid_attention_decode": [_P, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _LL, _F, _I, _P, _P],
@@ -1099,24 +1099,45 @@ def streams_broadcast(x: torch.Tensor, xs: torch.Tensor, streams: int) -> None:
     _call("gb_streams_broadcast", _ptr(x), _ptr(xs), n, streams, d, _stream())
 
 
+class WeightedRows:
+    """A branch output that exists only as its parts: y[r] = sum_k weight[r, k] * pair[r, k, :] + gate[r] * shared[r, :]
+    (``shared`` and ``gate`` optional; without a gate the shared row is added as it is). ``streams_step`` takes it in the
+    place of a stored y and forms the sum on the way."""
+    __slots__ = ("pair", "weight", "shared", "gate")
+
+    def __init__(self, pair: torch.Tensor, weight: torch.Tensor, shared: Optional[torch.Tensor] = None,
+                 gate: Optional[torch.Tensor] = None):
+        self.pair, self.weight, self.shared, self.gate = pair, weight, shared, gate
+
+
 def streams_step(xs: torch.Tensor, streams: int, *, fold=None, read: Optional[torch.Tensor] = None, norm=None,
                  h: Optional[torch.Tensor] = None, u_out: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
                  positions: Optional[torch.Tensor] = None) -> None:
     """One pass over the rows of a residual kept as ``streams`` rows per token (xs float32 [n, streams * d]; one stream: the
     plain residual). ``fold`` = (y, mix, write): first x_t <- sum_s mix[s, t] x_s + write[t] * y for all streams at once (y
-    float32 [n, d]; stored back unless ``rows`` gathers). Then u = sum_s read[s] x_s (``read`` None: the plain sum), stored
-    as float32 into ``u_out`` and / or through the layer norm ``norm`` = (weight, bias or None, eps) into ``h`` (any
-    activation dtype). ``rows`` (int32) picks the input row of each output row; ``positions`` marks padding rows (< 0),
-    which are skipped."""
+    float32 [n, d], or a ``WeightedRows``; stored back unless ``rows`` gathers). Then u = sum_s read[s] x_s (``read`` None:
+    the plain sum), stored as float32 into ``u_out`` and / or through the layer norm ``norm`` = (weight, bias or None, eps)
+    into ``h`` (any activation dtype). ``rows`` (int32) picks the input row of each output row; ``positions`` marks padding
+    rows (< 0), which are skipped."""
     _cuda(xs, read, h, u_out, rows, positions)
     n_src = xs.shape[0]
     d = xs.shape[1] // streams
     assert xs.dtype == torch.float32 and xs.is_contiguous() and xs.shape[1] == streams * d
     n_out = rows.shape[0] if rows is not None else n_src
-    y = mix = write = None
+    y = mix = write = lazy = None
     if fold is not None:
         y, mix, write = fold
-        assert y.dtype == mix.dtype == write.dtype == torch.float32 and y.shape == (n_src, d) and y.stride(1) == 1
+        if isinstance(y, WeightedRows):
+            lazy, y = y, None
+            top = lazy.weight.shape[1]
+            _cuda(lazy.pair, lazy.weight, lazy.shared, lazy.gate)
+            assert lazy.pair.dtype == lazy.weight.dtype == torch.float32 and lazy.pair.shape == (n_src, top * d)
+            assert lazy.pair.is_contiguous() and lazy.weight.is_contiguous() and lazy.weight.shape[0] == n_src
+            assert lazy.shared is None or (lazy.shared.dtype == torch.float32 and lazy.shared.shape == (n_src, d) and lazy.shared.stride(1) == 1)
+            assert lazy.gate is None or (lazy.gate.dtype == torch.float32 and lazy.gate.numel() >= n_src)
+        else:
+            assert y.dtype == torch.float32 and y.shape == (n_src, d) and y.stride(1) == 1
+        assert mix.dtype == write.dtype == torch.float32
         assert mix.numel() == streams * streams and write.numel() == streams and mix.is_contiguous()
     w = b = None
     eps = 0.0
@@ -1126,7 +1147,10 @@ def streams_step(xs: torch.Tensor, streams: int, *, fold=None, read: Optional[to
         assert b is None or (b.dtype == torch.float32 and b.numel() == d)
     assert read is None or (read.dtype == torch.float32 and read.numel() == streams)
     assert u_out is None or (u_out.dtype == torch.float32 and u_out.shape == (n_out, d) and u_out.is_contiguous())
-    _call("gb_streams_step", _ptr(xs), streams, d, _ptr(y), y.stride(0) if y is not None else 0, _ptr(mix), _ptr(write), _ptr(read),
+    _call("gb_streams_step", _ptr(xs), streams, d, _ptr(y), y.stride(0) if y is not None else 0,
+          _ptr(lazy.pair) if lazy else 0, _ptr(lazy.weight) if lazy else 0, lazy.weight.shape[1] if lazy else 0,
+          _ptr(lazy.shared) if lazy else 0, lazy.shared.stride(0) if lazy and lazy.shared is not None else 0,
+          _ptr(lazy.gate) if lazy else 0, _ptr(mix), _ptr(write), _ptr(read),
           _ptr(w), _ptr(b), float(eps), _ptr(h), _dt(h) if h is not None else F32, _ptr(u_out), _ptr(rows), _ptr(positions),
           n_out, n_src, _stream())
 

@@ -172,11 +172,15 @@ class HyperConnectionBlock(Part):
         ctx.overwrite_output = bool(part.can_overwrite_output)
         if not ctx.overwrite_output:
             y.zero_()
+        # a part whose output is a weighted sum of rows may hand over the parts instead (``kernels.WeightedRows`` in
+        # ``ctx.weighted_rows``): the kernel that folds the output into the streams forms the sum on its way
+        ctx.accepts_weighted_rows, ctx.weighted_rows = True, None
         try:
             run(h, y)
         finally:
-            ctx.overwrite_output = False
-        ctx.pending_fold = (y, mixing.params["mix"], mixing.params["write"])
+            ctx.overwrite_output = ctx.accepts_weighted_rows = False
+        out, ctx.weighted_rows = (ctx.weighted_rows if ctx.weighted_rows is not None else y), None
+        ctx.pending_fold = (out, mixing.params["mix"], mixing.params["write"])
 
     def forward(self, ctx, xs, cache, writes_cache: bool, after_mixer=None) -> None:
         ctx.next_norm = ctx.prepared_norm = None      # no product of this layer completes residual rows

@@ -83,6 +83,11 @@ class RoutedExperts(FeedForward):
             # few rows (or float32): the chosen experts' matrices streamed once per (row, choice), many blocks each
             act = ctx.scratch("moe_act32", (n, self.top * self.ff), torch.float32)
             kernels.moe_expert_halves(h, p["w_up"], p["w_down"], self.E, choice, ctx.positions, act, pair)
+        if getattr(ctx, "overwrite_output", False) and getattr(ctx, "accepts_weighted_rows", False):
+            # whoever wired this branch forms the weighted sum itself, on its way over the rows (one launch and one trip
+            # to memory less): the output is handed over as its parts
+            ctx.weighted_rows = kernels.WeightedRows(pair, weight, shared_out, gate)
+            return
         kernels.moe_combine(pair, weight, shared_out, gate, ctx.positions, residual,
                             accumulate=not getattr(ctx, "overwrite_output", False))
 

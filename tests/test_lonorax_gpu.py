@@ -85,6 +85,19 @@ def test_streams_fold_read_norm_and_gather(S, d):
     np.testing.assert_allclose(got_xs[live], new.transpose(1, 0, 2)[live], atol=1e-5, rtol=1e-5)
     np.testing.assert_array_equal(got_xs[3], xs[3].astype(np.float32))
     assert float(h[3].abs().max()) == 0.0
+    # the same fold with y handed over as its parts: a weighted sum of rows plus a gated shared row
+    top = 3
+    pair, pw, gate = rng.standard_normal((n, top, d)), rng.uniform(0.2, 1.5, (n, top)), rng.uniform(0, 1, n)
+    shared = y - np.einsum("nk,nkd->nd", pw, pair)
+    shared /= gate[:, None]
+    for parts in (kernels.WeightedRows(_f32(pair.reshape(n, top * d)), _f32(pw), _f32(shared), _f32(gate)),
+                  kernels.WeightedRows(_f32(pair.reshape(n, top * d)), _f32(pw), _f32(shared * gate[:, None]), None)):
+        dev3 = _f32(xs.reshape(n, S * d))
+        h3 = torch.zeros((n, d), dtype=torch.float32, device=DEV)
+        kernels.streams_step(dev3, S, fold=(parts, _f32(mix), _f32(write)), read=_f32(read), norm=(_f32(w), _f32(b), eps), h=h3,
+                             positions=positions)
+        np.testing.assert_allclose(h3.cpu().numpy()[live], want_h[live], atol=2e-4, rtol=1e-4)
+        np.testing.assert_allclose(dev3.cpu().numpy().reshape(n, S, d)[live], new.transpose(1, 0, 2)[live], atol=1e-4, rtol=1e-4)
     # the end of the streams: gathered rows, the plain sum, a fold that is computed but not stored
     dev2 = _f32(xs.reshape(n, S * d))
     rows = _i32([7, 0, 0, 4])
