@@ -77,38 +77,9 @@ __device__ __forceinline__ int moe_warp_argmax(const float* v, int count, int la
     return at;
 }
 
-template <typename T>
-__global__ void __launch_bounds__(MOE_ROUTE_THREADS) moe_route_kernel(
-    const T* __restrict__ h, int d, const float* __restrict__ w_router, const float* __restrict__ correction,
-    const float* __restrict__ w_gate, const int* __restrict__ positions, int n, int E, int top, int groups, int keep,
-    float route_scale, int* __restrict__ choice_out, float* __restrict__ weight_out, float* __restrict__ gate_out) {
-    extern __shared__ __align__(16) float moe_smem[];
-    float* hx = moe_smem;                       // the row, float32
-    __shared__ float score[MOE_MAX_EXPERTS], choice[MOE_MAX_EXPERTS], run_score[MOE_MAX_EXPERTS];
-    __shared__ unsigned char kept[MOE_MAX_EXPERTS];
-    gb_pdl_launch_dependents();
-    gb_pdl_wait();
-    const int row = blockIdx.x;
-    if (row >= n || positions[row] < 0) return;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const T* src = h + (size_t)row * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) hx[i] = gb_to_float(src[i]);
-    __syncthreads();
-    for (int e = warp; e < E + (w_gate ? 1 : 0); e += (int)(blockDim.x >> 5)) {
-        if (e < E) {
-            const float z = moe_warp_dot<float>(w_router + (size_t)e * d, hx, d, lane);
-            if (lane == 0) {
-                const float s = moe_sigmoid(z);
-                score[e] = s;
-                choice[e] = s + (correction ? correction[e] : 0.f);
-            }
-        } else {
-            const float z = moe_warp_dot<float>(w_gate, hx, d, lane);
-            if (lane == 0) gate_out[row] = moe_sigmoid(z);
-        }
-    }
-    __syncthreads();
-    if (warp != 0) return;
+// The choice for one row, by one warp: `score`, `choice` (score + correction), `run_score` and `kept` are the row's arrays.
+__device__ __forceinline__ void moe_choose(const float* score, float* choice, float* run_score, unsigned char* kept, int E, int top,
+                                           int groups, int keep, float route_scale, int* choice_out, float* weight_out, int lane) {
     if (groups > 1 && keep < groups) {
         const int per = E / groups;
         for (int g = lane; g < groups; g += 32) {
@@ -135,12 +106,100 @@ __global__ void __launch_bounds__(MOE_ROUTE_THREADS) moe_route_kernel(
         const int e = moe_warp_argmax(choice, E, lane);
         __syncwarp();
         if (lane == 0) {
-            choice_out[(size_t)row * top + k] = e;                          // -1: fewer experts could be chosen than `top`
-            weight_out[(size_t)row * top + k] = e >= 0 ? score[e] * route_scale : 0.f;
+            choice_out[k] = e;                                               // -1: fewer experts could be chosen than `top`
+            weight_out[k] = e >= 0 ? score[e] * route_scale : 0.f;
             if (e >= 0) choice[e] = -INFINITY;
         }
         __syncwarp();
     }
+}
+
+// RB rows per block: a warp per expert (and one for the shared gate) reads its row of the router matrix once and dots it
+// with the block's RB rows; then a warp per row chooses. RB = 1 for a handful of rows (shortest chain), 8 for many (the
+// router matrix is read an eighth as often). EMAX bounds the experts (the arrays' size).
+template <typename T, int RB, int EMAX>
+__global__ void __launch_bounds__(RB > 1 ? MOE_ROUTE_THREADS / 2 : MOE_ROUTE_THREADS) moe_route_kernel(
+    const T* __restrict__ h, int d, const float* __restrict__ w_router, const float* __restrict__ correction,
+    const float* __restrict__ w_gate, const int* __restrict__ positions, int n, int E, int top, int groups, int keep,
+    float route_scale, int* __restrict__ choice_out, float* __restrict__ weight_out, float* __restrict__ gate_out) {
+    extern __shared__ __align__(16) float moe_smem[];
+    float* hx = moe_smem;                       // RB rows of d numbers (rows start 16-byte aligned: ldh is a multiple of 4)
+    const int ldh = (d + 3) & ~3;
+    __shared__ float score[RB][EMAX], choice[RB][EMAX], run_score[RB][EMAX];
+    __shared__ unsigned char kept[RB][EMAX];
+    gb_pdl_launch_dependents();
+    gb_pdl_wait();
+    const int row0 = blockIdx.x * RB;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = (int)(blockDim.x >> 5);
+    bool any = false;
+#pragma unroll
+    for (int r = 0; r < RB; ++r) {
+        const int row = row0 + r;
+        const bool live = row < n && positions[row] >= 0;
+        any = any || live;
+        const T* src = h + (size_t)(live ? row : 0) * d;
+        for (int i = threadIdx.x; i < d; i += blockDim.x) hx[r * ldh + i] = live ? gb_to_float(src[i]) : 0.f;
+    }
+    if (!any) return;
+    __syncthreads();
+    for (int e = warp; e < E + (w_gate ? 1 : 0); e += warps) {
+        const float* wrow = e < E ? w_router + (size_t)e * d : w_gate;
+        float acc[RB];
+#pragma unroll
+        for (int r = 0; r < RB; ++r) acc[r] = 0.f;
+        if (d % 4 == 0 && ((uintptr_t)wrow & 15) == 0) {
+#pragma unroll 4
+            for (int i = lane * 4; i < d; i += 128) {
+                const float4 v = *reinterpret_cast<const float4*>(wrow + i);
+#pragma unroll
+                for (int r = 0; r < RB; ++r) {
+                    const float4 x = *reinterpret_cast<const float4*>(hx + r * ldh + i);
+                    acc[r] = fmaf(v.x, x.x, acc[r]); acc[r] = fmaf(v.y, x.y, acc[r]);
+                    acc[r] = fmaf(v.z, x.z, acc[r]); acc[r] = fmaf(v.w, x.w, acc[r]);
+                }
+            }
+        } else {
+            for (int i = lane; i < d; i += 32) {
+                const float v = wrow[i];
+#pragma unroll
+                for (int r = 0; r < RB; ++r) acc[r] = fmaf(v, hx[r * ldh + i], acc[r]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < RB; ++r) {
+            const float z = gb_warp_sum(acc[r]);
+            const int row = row0 + r;
+            if (lane == 0 && row < n && positions[row] >= 0) {
+                const float sg = moe_sigmoid(z);
+                if (e < E) {
+                    score[r][e] = sg;
+                    choice[r][e] = sg + (correction ? correction[e] : 0.f);
+                } else {
+                    gate_out[row] = sg;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    for (int r = warp; r < RB; r += warps) {
+        const int row = row0 + r;
+        if (row < n && positions[row] >= 0)
+            moe_choose(score[r], choice[r], run_score[r], kept[r], E, top, groups, keep, route_scale, choice_out + (size_t)row * top,
+                       weight_out + (size_t)row * top, lane);
+    }
+}
+
+template <typename T, int RB, int EMAX>
+static void moe_route_launch(const void* h, int d, const float* w_router, const float* correction, const float* w_gate,
+                             const int* positions, int n, int E, int top, int groups, int keep, float route_scale, int* choice_out,
+                             float* weight_out, float* gate_out, cudaStream_t stream) {
+    const size_t smem = (size_t)RB * ((d + 3) & ~3) * 4;
+    int warps = E + (w_gate ? 1 : 0);
+    const int most = (RB > 1 ? MOE_ROUTE_THREADS / 2 : MOE_ROUTE_THREADS) / 32, least = RB > 4 ? RB : 4;
+    warps = warps < least ? least : (warps > most ? most : warps);
+    if (smem > 32 * 1024) cudaFuncSetAttribute(moe_route_kernel<T, RB, EMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    gb_launch(GB_PDL_ELEMENTWISE, moe_route_kernel<T, RB, EMAX>, dim3(gb_ceil_div(n, RB)), dim3(32 * warps), smem, stream, (const T*)h, d,
+              w_router, correction, w_gate, positions, n, E, top, groups, keep, route_scale, choice_out, weight_out, gate_out);
 }
 
 GB_EXPORT int gb_moe_route(const void* h, int h_dtype, int d, const float* w_router, const float* correction, const float* w_gate,
@@ -152,24 +211,19 @@ GB_EXPORT int gb_moe_route(const void* h, int h_dtype, int d, const float* w_rou
                keep);
     GB_REQUIRE((size_t)d * 4 <= 160 * 1024, "gb_moe_route: a row of %d numbers does not fit shared memory", d);
     GB_REQUIRE(w_gate == nullptr || gate_out != nullptr, "gb_moe_route: a gate needs its output");
+    GB_REQUIRE(h_dtype == GB_F32 || h_dtype == GB_BF16, "gb_moe_route: unsupported dtype %d", h_dtype);
     if (n == 0) return 0;
-    const size_t smem = (size_t)d * 4;
-    int warps = E + (w_gate ? 1 : 0);
-    warps = warps < 4 ? 4 : (warps > MOE_ROUTE_THREADS / 32 ? MOE_ROUTE_THREADS / 32 : warps);
-    const dim3 block(32 * warps);
-    if (h_dtype == GB_F32) {
-        if (smem > 32 * 1024) cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        gb_launch(GB_PDL_ELEMENTWISE, moe_route_kernel<float>, dim3(n), block, smem, stream, (const float*)h, d, w_router,
-                  correction, w_gate, positions, n, E, top, groups, keep, route_scale, choice_out, weight_out, gate_out);
-    } else if (h_dtype == GB_BF16) {
-        if (smem > 32 * 1024)
-            cudaFuncSetAttribute(moe_route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        gb_launch(GB_PDL_ELEMENTWISE, moe_route_kernel<__nv_bfloat16>, dim3(n), block, smem, stream,
-                  (const __nv_bfloat16*)h, d, w_router, correction, w_gate, positions, n, E, top, groups, keep, route_scale, choice_out,
-                  weight_out, gate_out);
-    } else {
-        GB_REQUIRE(false, "gb_moe_route: unsupported dtype %d", h_dtype);
-    }
+    // eight rows per block when there are many rows, the experts are few enough for the block's arrays and eight rows fit
+    const bool many = n > 256 && E <= 128 && (size_t)8 * ((d + 3) & ~3) * 4 <= 160 * 1024;      // (below: too few blocks to fill the GPU)
+#define MOE_ROUTE_GO(T)                                                                                                              \
+    if (many)                                                                                                                        \
+        moe_route_launch<T, 8, 128>(h, d, w_router, correction, w_gate, positions, n, E, top, groups, keep, route_scale, choice_out,  \
+                                    weight_out, gate_out, stream);                                                                   \
+    else                                                                                                                             \
+        moe_route_launch<T, 1, MOE_MAX_EXPERTS>(h, d, w_router, correction, w_gate, positions, n, E, top, groups, keep, route_scale,  \
+                                                choice_out, weight_out, gate_out, stream);
+    if (h_dtype == GB_F32) { MOE_ROUTE_GO(float) } else { MOE_ROUTE_GO(__nv_bfloat16) }
+#undef MOE_ROUTE_GO
     return gb_check_launch("gb_moe_route");
 }
 

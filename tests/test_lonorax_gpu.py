@@ -408,10 +408,10 @@ def _route_plain(h, Wr, corr, router):
 
 @pytest.mark.parametrize("E, top, groups, d", [(6, 2, (3, 2), 56), (16, 4, (4, 3), 128), (5, 1, None, 33), (4, 1, (4, 2), 32), (8, 8, None, 40),
                                               (64, 6, (8, 3), 96)])
-def test_router_choice_and_weights(E, top, groups, d):
+@pytest.mark.parametrize("n", [50, 300])                      # (300: the form that takes eight rows per block)
+def test_router_choice_and_weights(E, top, groups, d, n):
     from glassbox_b200 import kernels
     rng = np.random.default_rng(E * 10 + top)
-    n = 50
     h = rng.standard_normal((n, d))
     Wr, corr, wg = rng.standard_normal((E, d)) * 2 / np.sqrt(d), rng.standard_normal(E) * 0.5 - 0.7, rng.standard_normal(d) / np.sqrt(d)
     router = {"experts": E, "top": top, "scale": 1.7}
